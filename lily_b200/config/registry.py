@@ -46,6 +46,14 @@ def supported_architectures() -> List[str]:
     return sorted(_ARCHITECTURES)
 
 
+def architecture_names(config_json: Dict[str, Any]) -> List[str]:
+    """The names a config.json offers for its model: the ``architectures`` list, or a single ``architecture``."""
+    names = config_json.get("architectures")
+    if not names and config_json.get("architecture"):
+        names = [config_json["architecture"]]
+    return [str(n) for n in names or []]
+
+
 def resolve_architecture(architectures: Optional[Sequence[str]]) -> Architecture:
     _load_builtins()
     for name in architectures or []:

@@ -33,6 +33,9 @@ struct AttnArgs {
     const float* sin_t;
     int rd;                   // rotary width
     int write_kv;             // 0: the cache already holds this position (a layer that reads another layer's cache)
+    float softcap;            // > 0: scores become softcap * tanh(score * scale / softcap) before the mask and the softmax
+    int dv;                   // value head size where it differs from d (CUDA-core kernels; 0: d); a page then holds its
+                              // keys [kv_heads, page_size, d] followed by its values [kv_heads, page_size, dv]
     int stages;               // decode, tensor-core kernel: key/value tiles a block keeps in shared memory (0: the default, 2;
                               // 3: two blocks a SM instead of three, each with two tiles in flight; head sizes up to 128)
 };

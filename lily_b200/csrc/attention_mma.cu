@@ -416,7 +416,9 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
             cp_async_commit();
         }
     }
-    const float sl2 = a.scale * 1.4426950408889634f;       // scores are kept in units of log2(e)
+    // scores are kept in units of log2(e); with a soft cap they are capped first and then carry no further scale
+    const float cap = a.softcap, cap_in = cap > 0.f ? a.scale / cap : 0.f;
+    const float sl2 = (cap > 0.f ? 1.f : a.scale) * 1.4426950408889634f;
 
     for (int t = 0; t < ntiles; ++t) {
         const int buf = t % STAGES;
@@ -443,6 +445,14 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
                 ldmatrix_x4(smem_u32(kt + swz<D>(krow, kk * 2 + ((lane >> 3) & 1))), b0, b1, b2, b3);
                 mma_bf16(s[2 * jp], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
                 mma_bf16(s[2 * jp + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+            }
+        }
+
+        if (cap > 0.f) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] = cap * tanhf(s[j][e] * cap_in);
             }
         }
 
@@ -807,7 +817,8 @@ LILY_API int lily_attention_decode_spans(unsigned long long* out, int blocks) {
 LILY_API int lily_attention_prefill_mma(const void* q, const void* kv, void* out, const int* block_table,
                                         int bt_stride, const int* cu_seqlens, const int* prefix_lens,
                                         const int* tile_req, const int* tile_start, int tiles, int nq, int nkv,
-                                        int d, int page_size, int window, float scale, cudaStream_t stream) {
+                                        int d, int page_size, int window, float scale, float softcap,
+                                        cudaStream_t stream) {
     if (tiles == 0) return 0;
     LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill: %d query heads over %d kv heads", nq, nkv);
     LILY_REQUIRE(nq <= 65535 && page_size > 0, "attention_prefill: nq=%d page_size=%d", nq, page_size);
@@ -815,6 +826,7 @@ LILY_API int lily_attention_prefill_mma(const void* q, const void* kv, void* out
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
     a.cu_seqlens = cu_seqlens; a.prefix_lens = prefix_lens; a.tile_req = tile_req; a.tile_start = tile_start;
     a.splits = 1; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
+    a.softcap = softcap;
     bool merged = false;
     int rc = mma::dispatch<false>(a, dim3(tiles, nq), stream, &merged);
     if (rc) return rc;
@@ -870,8 +882,9 @@ static int decode_mma(AttnArgs& a, const void* q, const void* kv, void* out, con
 LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out, const int* block_table,
                                        int bt_stride, const int* seq_lens, float* scratch, int requests, int splits,
                                        int nq, int nkv, int d, int page_size, int window, float scale, int stages,
-                                       cudaStream_t stream) {
+                                       float softcap, cudaStream_t stream) {
     AttnArgs a{};
+    a.softcap = softcap;
     return decode_mma(a, q, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv, d, page_size,
                       window, scale, stages, stream);
 }
@@ -886,7 +899,7 @@ LILY_API int lily_attention_decode_mma_fused(const void* qkv, int qkv_planes, si
                                              void* kv, void* out, const int* block_table, int bt_stride,
                                              const int* seq_lens, float* scratch, int requests, int splits, int nq,
                                              int nkv, int d, int page_size, int window, float scale, int stages,
-                                             cudaStream_t stream) {
+                                             float softcap, cudaStream_t stream) {
     LILY_REQUIRE(qkv != nullptr && qkv_planes >= 1 && (qkv_dtype == kF32 || qkv_planes == 1),
                  "attention_decode_fused: %d planes of dtype %d", qkv_planes, qkv_dtype);
     LILY_REQUIRE(rd >= 0 && rd <= d && rd % 2 == 0, "attention_decode_fused: rotary_dim %d does not fit head_dim %d", rd, d);
@@ -896,6 +909,7 @@ LILY_API int lily_attention_decode_mma_fused(const void* qkv, int qkv_planes, si
     a.qkv = qkv; a.qkv_planes = qkv_planes; a.qkv_stride = qkv_stride; a.qkv_f32 = qkv_dtype == kF32;
     a.q_gain = q_gain; a.k_gain = k_gain; a.gain_f32 = gain_dtype == kF32; a.eps = eps;
     a.cos_t = cos_t; a.sin_t = sin_t; a.rd = cos_t ? rd : 0; a.write_kv = write_kv;
+    a.softcap = softcap;
     return decode_mma(a, nullptr, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv, d,
                       page_size, window, scale, stages, stream);
 }

@@ -3,7 +3,9 @@
 // takes the shape.
 //
 // Cache layout of one layer: [pages, 2 (keys, values), kv_heads, page_size, head_dim]; a
-// request's block table gives the page of each run of page_size positions.
+// request's block table gives the page of each run of page_size positions.  Values may have a head
+// size of their own (`dv`): a page is then its keys [kv_heads, page_size, d] followed by its values
+// [kv_heads, page_size, dv], and outputs have dv columns a head.
 //
 //  * prefill: grid (query tiles, query heads).  A tile is up to 32 consecutive new tokens of one
 //    request; their keys are the request's cached prefix and the new tokens up to each query
@@ -12,7 +14,7 @@
 //    query heads that share a kv head are the rows; the keys are cut into `splits` ranges whose
 //    partial (max, sum, output) go to scratch and are merged by the combine kernel.
 //
-// Scores q.k * scale, keys visible when key position <= query position (and > query position -
+// Scores q.k * scale (soft-capped to softcap * tanh(. / softcap) when a cap is given), keys visible when key position <= query position (and > query position -
 // window when a window is given), softmax and p.v in float32: the formulas of
 // lily/layers/attention/torch_native_backend.py:31-37,52-77; the split over keys follows
 // lily/layers/attention/triton_ops/decode_attention.py:21-157, the prefix + new tokens form
@@ -32,11 +34,11 @@ template <typename T, int DCH, bool DECODE>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const AttnArgs a) {
     extern __shared__ float smem[];
-    const int d = a.d;
+    const int d = a.d, dv = a.dv;
     float* Qs = smem;                          // [ROWS][d]
     float* Ks = Qs + ROWS * d;                 // [KEYS][d + 1]
-    float* Vs = Ks + KEYS * (d + 1);           // [KEYS][d]
-    float* Ps = Vs + KEYS * d;                 // [WARPS][RPW][KEYS]
+    float* Vs = Ks + KEYS * (d + 1);           // [KEYS][dv]
+    float* Ps = Vs + KEYS * dv;                // [WARPS][RPW][KEYS]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const T* q = (const T*)a.q;
     const T* kv = (const T*)a.kv;
@@ -105,8 +107,9 @@ attention_simt_kernel(const AttnArgs a) {
     }
 
     const int* table = a.block_table + (size_t)req * a.bt_stride;
-    const size_t head_stride = (size_t)a.page_size * d;            // one head's tile in a page
-    const size_t page_stride = 2 * (size_t)a.nkv * head_stride;
+    const size_t khead = (size_t)a.page_size * d, vhead = (size_t)a.page_size * dv;     // one head's tiles in a page
+    const size_t page_stride = (size_t)a.nkv * (khead + vhead);
+    const float cap = a.softcap, cap_in = cap > 0.f ? a.scale / cap : 0.f;
 
     for (int kb = kbeg; kb < kend; kb += KEYS) {
         __syncthreads();
@@ -115,17 +118,14 @@ attention_simt_kernel(const AttnArgs a) {
             const int kpos = kb + j;
             if (kpos < kend) {
                 const int page = table[kpos / a.page_size];
-                const T* ksrc = kv + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)(kpos % a.page_size) * d;
-                const T* vsrc = ksrc + (size_t)a.nkv * head_stride;
-                for (int c = lane; c < d; c += 32) {
-                    Ks[j * (d + 1) + c] = to_float(ksrc[c]);
-                    Vs[j * d + c] = to_float(vsrc[c]);
-                }
+                const T* base = kv + (size_t)page * page_stride;
+                const T* ksrc = base + (size_t)kvh * khead + (size_t)(kpos % a.page_size) * d;
+                const T* vsrc = base + (size_t)a.nkv * khead + (size_t)kvh * vhead + (size_t)(kpos % a.page_size) * dv;
+                for (int c = lane; c < d; c += 32) Ks[j * (d + 1) + c] = to_float(ksrc[c]);
+                for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = to_float(vsrc[c]);
             } else {
-                for (int c = lane; c < d; c += 32) {
-                    Ks[j * (d + 1) + c] = 0.f;
-                    Vs[j * d + c] = 0.f;
-                }
+                for (int c = lane; c < d; c += 32) Ks[j * (d + 1) + c] = 0.f;
+                for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = 0.f;
             }
         }
         __syncthreads();
@@ -148,7 +148,7 @@ attention_simt_kernel(const AttnArgs a) {
         for (int i = 0; i < RPW; ++i) {
             const bool seen = row_ok[i] && kpos < kend && kpos <= row_pos[i] &&
                               (a.window <= 0 || kpos > row_pos[i] - a.window);
-            const float sv = seen ? s[i] * a.scale : -INFINITY;
+            const float sv = seen ? (cap > 0.f ? cap * tanhf(s[i] * cap_in) : s[i] * a.scale) : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(sv));
             float p = 0.f, alpha = 1.f;
             if (m_new > -INFINITY) {
@@ -168,7 +168,7 @@ attention_simt_kernel(const AttnArgs a) {
 #pragma unroll
             for (int c = 0; c < DCH; ++c) {
                 const int col = lane + 32 * c;
-                v[c] = col < d ? Vs[j * d + col] : 0.f;
+                v[c] = col < dv ? Vs[j * dv + col] : 0.f;
             }
 #pragma unroll
             for (int i = 0; i < RPW; ++i) {
@@ -188,7 +188,7 @@ attention_simt_kernel(const AttnArgs a) {
 #pragma unroll
             for (int c = 0; c < DCH; ++c) {
                 const int col = lane + 32 * c;
-                if (col < d) a.part_o[base * d + col] = acc[i][c];
+                if (col < dv) a.part_o[base * dv + col] = acc[i][c];
             }
             if (lane == 0) {
                 a.part_ml[base * 2] = m[i];
@@ -196,11 +196,11 @@ attention_simt_kernel(const AttnArgs a) {
             }
         } else {
             const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
-            T* dst = out + ((size_t)row_tok[i] * a.nq + row_head[i]) * d;
+            T* dst = out + ((size_t)row_tok[i] * a.nq + row_head[i]) * dv;
 #pragma unroll
             for (int c = 0; c < DCH; ++c) {
                 const int col = lane + 32 * c;
-                if (col < d) dst[col] = from_float<T>(acc[i][c] * inv);
+                if (col < dv) dst[col] = from_float<T>(acc[i][c] * inv);
             }
         }
     }
@@ -291,12 +291,12 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     }
 }
 
-static size_t smem_bytes(int d) { return sizeof(float) * ((size_t)ROWS * d + KEYS * (d + 1) + KEYS * d + ROWS * KEYS); }
+static size_t smem_bytes(int d, int dv) { return sizeof(float) * ((size_t)ROWS * d + KEYS * (d + 1) + KEYS * dv + ROWS * KEYS); }
 
 template <typename T, bool DECODE>
 static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
-    const int dch = (a.d + 31) / 32;
-    const size_t smem = smem_bytes(a.d);
+    const int dch = (a.dv + 31) / 32;              // output columns a lane owns
+    const size_t smem = smem_bytes(a.d, a.dv);
 #define CASE(N)                                                                                          \
     case N: {                                                                                            \
         auto kern = attention_simt_kernel<T, N, DECODE>;                                                 \
@@ -312,16 +312,17 @@ static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
     switch (dch) {
         CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8)
         default:
-            set_error("attention: head_dim %d is beyond the 256 this kernel takes", a.d);
+            set_error("attention: value head size %d is beyond the 256 this kernel takes", a.dv);
             return 1;
     }
 #undef CASE
     return 0;
 }
 
-static int check_common(const char* name, int nq, int nkv, int d, int page_size) {
+static int check_common(const char* name, int nq, int nkv, int d, int page_size, int dv) {
     LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "%s: %d query heads do not group over %d kv heads", name, nq, nkv);
     LILY_REQUIRE(d > 0 && d <= 256, "%s: head_dim %d is outside 1..256", name, d);
+    LILY_REQUIRE(dv >= 0 && dv <= 256, "%s: value head size %d is outside 1..256", name, dv);
     LILY_REQUIRE(page_size > 0, "%s: page_size %d", name, page_size);
     return 0;
 }
@@ -334,14 +335,15 @@ LILY_API int lily_attention_prefill_simt(const void* q, const void* kv, void* ou
                                          int bt_stride, const int* cu_seqlens, const int* prefix_lens,
                                          const int* tile_req, const int* tile_start, int tiles, int nq, int nkv,
                                          int d, int page_size, int window, float scale, int dtype,
-                                         cudaStream_t stream) {
+                                         float softcap, int dv, cudaStream_t stream) {
     if (tiles == 0) return 0;
-    if (check_common("attention_prefill", nq, nkv, d, page_size)) return 1;
+    if (check_common("attention_prefill", nq, nkv, d, page_size, dv)) return 1;
     LILY_REQUIRE(nq <= 65535, "attention_prefill: %d query heads", nq);
     AttnArgs a{};
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
     a.cu_seqlens = cu_seqlens; a.prefix_lens = prefix_lens; a.tile_req = tile_req; a.tile_start = tile_start;
     a.splits = 1; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
+    a.softcap = softcap; a.dv = dv > 0 ? dv : d;
     dim3 grid(tiles, nq);
     int rc = dtype == kBF16 ? launch<__nv_bfloat16, false>(a, grid, stream) : launch<float, false>(a, grid, stream);
     if (rc) return rc;
@@ -375,29 +377,30 @@ LILY_API size_t lily_attention_decode_scratch_floats(int requests, int nq, int d
 LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out, const int* block_table,
                                         int bt_stride, const int* seq_lens, float* scratch, int requests,
                                         int splits, int nq, int nkv, int d, int page_size, int window,
-                                        float scale, int dtype, cudaStream_t stream) {
+                                        float scale, int dtype, float softcap, int dv, cudaStream_t stream) {
     if (requests == 0) return 0;
-    if (check_common("attention_decode", nq, nkv, d, page_size)) return 1;
+    if (check_common("attention_decode", nq, nkv, d, page_size, dv)) return 1;
+    const int d_out = dv > 0 ? dv : d;
     LILY_REQUIRE(splits >= 1 && splits <= 65535, "attention_decode: %d splits", splits);
     LILY_REQUIRE(splits == 1 || scratch != nullptr, "attention_decode: splits need scratch");
     const int group = nq / nkv, chunks = (group + ROWS - 1) / ROWS;
     AttnArgs a{};
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
     a.seq_lens = seq_lens; a.splits = splits; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size;
-    a.window = window; a.scale = scale;
+    a.window = window; a.scale = scale; a.softcap = softcap; a.dv = d_out;
     a.part_o = scratch;
-    a.part_ml = scratch ? scratch + (size_t)requests * nq * splits * d : nullptr;
+    a.part_ml = scratch ? scratch + (size_t)requests * nq * splits * d_out : nullptr;
     dim3 grid(requests, nkv * chunks, splits);
     LILY_REQUIRE(grid.y <= 65535, "attention_decode: %d kv heads", nkv);
     int rc = dtype == kBF16 ? launch<__nv_bfloat16, true>(a, grid, stream) : launch<float, true>(a, grid, stream);
     if (rc) return rc;
     LILY_CHECK_LAUNCH("attention_decode");
     if (splits > 1) {
-        dim3 cgrid(requests, nq), cblock(128, combine_staged(splits, d) ? COMBINE_ROWS : 1);
+        dim3 cgrid(requests, nq), cblock(128, combine_staged(splits, d_out) ? COMBINE_ROWS : 1);
         if (dtype == kBF16)
-            launch_pdl(attention_combine_kernel<__nv_bfloat16>, cgrid, cblock, 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (__nv_bfloat16*)out, nq, d, splits);
+            launch_pdl(attention_combine_kernel<__nv_bfloat16>, cgrid, cblock, 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (__nv_bfloat16*)out, nq, d_out, splits);
         else
-            launch_pdl(attention_combine_kernel<float>, cgrid, cblock, 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (float*)out, nq, d, splits);
+            launch_pdl(attention_combine_kernel<float>, cgrid, cblock, 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (float*)out, nq, d_out, splits);
         LILY_CHECK_LAUNCH("attention_combine");
     }
     return 0;

@@ -1,0 +1,113 @@
+// Kernels that join the outputs of sublayers which read the same input:
+//
+//   sigmoid gate:   out[t][c] *= sigmoid(gate[t][c])                    (an output gate ahead of a projection)
+//   normed mean:    out[t] = scale * sum_k rms(in_k[t]) * gain_k  (+ add[t])      as float32
+//
+// where rms(v) = v / sqrt(mean(v^2) + eps).  Every input may be the activation dtype, float32, or the
+// float32 partial sums of a split-k product (added up in order while they are read); sums, roots and the
+// result are float32.
+#include "common.cuh"
+
+namespace lily {
+
+struct Operand {
+    const void* p;
+    int bf16;
+    int splits;
+    size_t stride;
+    __device__ __forceinline__ float operator()(size_t i) const {
+        if (bf16) return __bfloat162float(((const __nv_bfloat16*)p)[i]);
+        const float* f = (const float*)p;
+        float v = f[i];
+        for (int s = 1; s < splits; ++s) v += f[i + (size_t)s * stride];
+        return v;
+    }
+};
+
+constexpr int MEAN_MAX = 4;
+
+struct NormedMeanArgs {
+    Operand in[MEAN_MAX];
+    const float* gain[MEAN_MAX];
+    int count;
+    Operand add;
+    float* out;
+    int width;
+    float eps, scale;
+};
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ out, const Operand gate, size_t total) {
+    pdl_enter_small();
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+        out[i] = from_float<T>(to_float(out[i]) / (1.f + expf(-gate(i))));
+}
+
+// One block a token.
+__global__ void normed_mean_kernel(const NormedMeanArgs a) {
+    __shared__ float red[33];
+    pdl_enter_small();
+    const size_t base = (size_t)blockIdx.x * a.width;
+    float inv[MEAN_MAX];
+#pragma unroll
+    for (int k = 0; k < MEAN_MAX; ++k) {
+        inv[k] = 0.f;
+        if (k < a.count) {
+            float ssq = 0.f;
+            for (int i = threadIdx.x; i < a.width; i += blockDim.x) {
+                const float v = a.in[k](base + i);
+                ssq = fmaf(v, v, ssq);
+            }
+            inv[k] = rsqrtf(block_sum(ssq, red) / (float)a.width + a.eps);
+        }
+    }
+    for (int i = threadIdx.x; i < a.width; i += blockDim.x) {
+        float o = 0.f;
+#pragma unroll
+        for (int k = 0; k < MEAN_MAX; ++k)
+            if (k < a.count) o += (a.in[k](base + i) * inv[k]) * a.gain[k][i];
+        o *= a.scale;
+        if (a.add.p) o += a.add(base + i);
+        a.out[base + i] = o;
+    }
+}
+
+}  // namespace lily
+
+using namespace lily;
+
+LILY_API int lily_sigmoid_gate(void* out, int out_dtype, const void* gate, int gate_dtype, int gate_splits,
+                               size_t gate_stride, size_t total, cudaStream_t stream) {
+    if (total == 0) return 0;
+    LILY_REQUIRE(gate_splits >= 1 && (gate_splits == 1 || gate_dtype == kF32), "sigmoid_gate: only float32 partial sums come in several splits");
+    const Operand g{gate, gate_dtype == kBF16, gate_splits, gate_stride};
+    const int blocks = (int)((total + 255) / 256 < (size_t)sm_count() * 16 ? (total + 255) / 256 : (size_t)sm_count() * 16);
+    if (out_dtype == kBF16) launch_pdl(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, g, total);
+    else launch_pdl(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, g, total);
+    LILY_CHECK_LAUNCH("sigmoid_gate");
+    return 0;
+}
+
+LILY_API int lily_normed_mean_max() { return MEAN_MAX; }
+
+// ins / dtypes / splits / strides / gains: `count` entries each; `add` may be null.
+LILY_API int lily_normed_mean(const void* const* ins, const int* dtypes, const int* splits, const size_t* strides,
+                              const float* const* gains, int count, const void* add, int add_dtype, int add_splits,
+                              size_t add_stride, float* out, int tokens, int width, float eps, float scale,
+                              cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LILY_REQUIRE(count >= 1 && count <= MEAN_MAX, "normed_mean: %d inputs (1 to %d)", count, MEAN_MAX);
+    NormedMeanArgs a{};
+    for (int k = 0; k < count; ++k) {
+        LILY_REQUIRE(splits[k] >= 1 && (splits[k] == 1 || dtypes[k] == kF32), "normed_mean: only float32 partial sums come in several splits");
+        a.in[k] = Operand{ins[k], dtypes[k] == kBF16, splits[k], strides[k]};
+        a.gain[k] = gains[k];
+    }
+    a.count = count;
+    a.add = Operand{add, add_dtype == kBF16, add_splits < 1 ? 1 : add_splits, add_stride};
+    a.out = out; a.width = width; a.eps = eps; a.scale = scale;
+    launch_pdl(normed_mean_kernel, dim3(tokens), dim3(width >= 2048 ? 512 : 256), 0, stream, a);
+    LILY_CHECK_LAUNCH("normed_mean");
+    return 0;
+}

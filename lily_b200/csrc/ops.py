@@ -27,22 +27,27 @@ _SIGNATURES = {
     "lily_logit_transform": [_vp, _sz, _f, _f, _vp],
     "lily_scatter_tokens": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _sz, _vp],
-    "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _vp],
+    "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _i, _vp],
     "lily_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "lily_qk_norm_rope_write": [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                _i, _i, _i, _i, _i, _sz, _vp],
+                                _i, _i, _i, _i, _i, _sz, _i, _vp],
     "lily_skinny_gemm": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "lily_skinny_swiglu": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "lily_cast": [_vp, _i, _vp, _i, _sz, _vp],
     "lily_gemm_fp32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
-    "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
+    "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp],
     "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
-    "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _vp],
     "lily_attention_decode_mma_fused": [_vp, _i, _sz, _i, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp,
-                                        _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+                                        _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _vp],
+    "lily_sigmoid_gate": [_vp, _i, _vp, _i, _i, _sz, _sz, _vp],
+    "lily_normed_mean": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _sz, _vp, _i, _i, _f, _f, _vp],
+    "lily_causal_conv_silu": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _vp],
+    "lily_ssd_scan": [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "lily_gated_group_rmsnorm": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_top_logprobs": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -82,6 +87,7 @@ def library():
         lib.lily_top_logprobs_cap.restype = _i
         lib.lily_attention_decode_scratch_floats.argtypes = [_i, _i, _i, _i]
         lib.lily_attention_decode_scratch_floats.restype = _sz
+        lib.lily_normed_mean_max.restype = _i
         _lib = lib
     return _lib
 
@@ -212,18 +218,24 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     return out
 
 
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
 def silu_mul(gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
-             block: Optional[int] = None) -> torch.Tensor:
-    """``silu(gate) * up`` of ``gate_up`` [tokens, 2I] = [all gate | all up], or, with ``block``,
-    alternating runs of ``block`` gate and ``block`` up columns.  ``gate_up`` may be float32 partial
+             block: Optional[int] = None, activation: str = "silu") -> torch.Tensor:
+    """``act(gate) * up`` of ``gate_up`` [tokens, 2I] = [all gate | all up], or, with ``block``,
+    alternating runs of ``block`` gate and ``block`` up columns; ``activation`` is "silu" or "gelu_tanh"
+    (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))).  ``gate_up`` may be float32 partial
     sums [splits, tokens, 2I], in which case ``out_dtype`` says what to write."""
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"no gate activation {activation!r}; have {sorted(ACTIVATIONS)}")
     _dev(gate_up, out)
     n, two_i = gate_up.shape[-2:]
     splits, stride = _summed(gate_up, n, two_i, "silu_mul")
     if out is None:
         out = torch.empty((n, two_i // 2), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
     _call("lily_silu_mul", _p(gate_up), _p(out), n, two_i // 2, int(block or two_i // 2), _dt(out), _dt(gate_up), splits,
-          stride, _stream())
+          stride, ACTIVATIONS[activation], _stream())
     return out
 
 
@@ -231,17 +243,18 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain
                        eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                        positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
                        kv_layer: torch.Tensor, nq: int, nkv: int, d: int, rotary_dim: int, page_size: int,
-                       write_kv: bool = True, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       write_kv: bool = True, q_out: Optional[torch.Tensor] = None, dv: Optional[int] = None) -> torch.Tensor:
     """Per-head RMSNorm of q and k (when gains are given), rotation by the tables, q to ``q_out``
     [tokens, nq * d], k and v into the token's place in its page of ``kv_layer``.  ``qkv`` is
-    [tokens, (nq + 2 nkv) d] in the cache's dtype or float32 partial sums [splits, tokens, ...]."""
+    [tokens, (nq + nkv) d + nkv dv] in the cache's dtype or float32 partial sums [splits, tokens, ...]; value
+    heads have ``dv`` features (default d; see ``cache_layer_fits`` for the page layout)."""
     _dev(qkv, q_gain, k_gain, cos, sin, positions, token_req, block_table, kv_layer, q_out)
     n = qkv.shape[-2]
-    splits, stride = _summed(qkv, n, (nq + 2 * nkv) * d, "qk_norm_rope_write qkv")
+    dv = int(dv or d)
+    splits, stride = _summed(qkv, n, (nq + nkv) * d + nkv * dv, "qk_norm_rope_write qkv")
     if qkv.dtype not in (kv_layer.dtype, torch.float32):
         raise KernelError(f"cache dtype {kv_layer.dtype} differs from activations {qkv.dtype}")
-    if tuple(kv_layer.shape[1:]) != (2, nkv, page_size, d):
-        raise KernelError(f"cache layer shape {tuple(kv_layer.shape)} does not fit kv_heads={nkv} page={page_size} d={d}")
+    cache_layer_fits(kv_layer, nkv, page_size, d, dv)
     if cos is not None and (cos.dtype != torch.float32 or cos.shape[-1] != rotary_dim // 2):
         raise KernelError("rotation tables must be float32 [positions, rotary_dim / 2]")
     if q_gain is not None and q_gain.dtype != k_gain.dtype:
@@ -251,8 +264,18 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain
     _call("lily_qk_norm_rope_write", _p(qkv), _p(q_gain), _p(k_gain), float(eps), _p(cos), _p(sin),
           _i32(positions, "positions"), _i32(token_req, "token_req"), _i32(block_table, "block_table"),
           block_table.shape[-1], _p(kv_layer), _p(q_out), n, nq, nkv, d, rotary_dim, page_size, int(write_kv),
-          _dt(kv_layer), _dt(q_gain) if q_gain is not None else _F32, _dt(qkv), splits, stride, _stream())
+          _dt(kv_layer), _dt(q_gain) if q_gain is not None else _F32, _dt(qkv), splits, stride, dv, _stream())
     return q_out
+
+
+def cache_layer_fits(kv_layer: torch.Tensor, nkv: int, page_size: int, d: int, dv: int) -> None:
+    """A cache layer is [pages, 2, kv_heads, page_size, d] when keys and values have one head size, else
+    [pages, kv_heads * page_size * (d + dv)]: a page's keys [kv_heads, page_size, d], then its values
+    [kv_heads, page_size, dv] (the first form is the second with dv == d)."""
+    want = (2, nkv, page_size, d) if dv == d else (nkv * page_size * (d + dv),)
+    if tuple(kv_layer.shape[1:]) != want:
+        raise KernelError(f"cache layer shape {tuple(kv_layer.shape)} does not fit kv_heads={nkv} page={page_size} "
+                          f"d={d} dv={dv}")
 
 
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
@@ -445,20 +468,23 @@ def uses_tensor_cores(dtype: torch.dtype, d: int) -> bool:
 TC_ATTENTION_MIN_TOKENS = 128
 
 
-def uses_tcgen05_attention(dtype: torch.dtype, d: int, page_size: int, new_tokens: int) -> bool:
+def uses_tcgen05_attention(dtype: torch.dtype, d: int, page_size: int, new_tokens: int, plain: bool = True) -> bool:
     """Whether prefill attention of this precision, head size, page size and number of new tokens
-    runs on the tcgen05 kernel (bfloat16, head size 128 or 64, pages of a multiple of 64 positions)."""
-    return (dtype == torch.bfloat16 and new_tokens >= TC_ATTENTION_MIN_TOKENS
+    runs on the tcgen05 kernel (bfloat16, head size 128 or 64, pages of a multiple of 64 positions, scores that
+    are only scaled: ``plain`` is False for soft-capped scores, which the mma.sync kernel takes)."""
+    return (plain and dtype == torch.bfloat16 and new_tokens >= TC_ATTENTION_MIN_TOKENS
             and bool(library().lily_attention_prefill_tc_takes(int(d), int(page_size))))
 
 
-def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size: int = 0, new_tokens: int = 0) -> int:
-    """New tokens per tile of the prefill kernel that will take this precision, head size, page
-    size and number of new tokens."""
+def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size: int = 0, new_tokens: int = 0,
+                      softcap: Optional[float] = None, dv: Optional[int] = None) -> int:
+    """New tokens per tile of the prefill kernel that will take this precision, head size (``dv`` for the values
+    where it differs), page size, number of new tokens and kind of scores."""
     lib = library()
-    if uses_tcgen05_attention(dtype, d, page_size, new_tokens):
+    same = dv is None or dv == d
+    if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens, plain=not softcap):
         return int(lib.lily_attention_prefill_tc_rows())
-    return int(lib.lily_attention_prefill_mma_rows() if uses_tensor_cores(dtype, d) else lib.lily_attention_prefill_simt_rows())
+    return int(lib.lily_attention_prefill_mma_rows() if same and uses_tensor_cores(dtype, d) else lib.lily_attention_prefill_simt_rows())
 
 
 def attention_tc_status() -> int:
@@ -469,8 +495,11 @@ def attention_tc_status() -> int:
 def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
                       prefix_lens: torch.Tensor, tile_req: torch.Tensor, tile_start: torch.Tensor, out: torch.Tensor,
                       nq: int, nkv: int, d: int, page_size: int, scale: float, window: Optional[int] = None,
-                      tile_rows: Optional[int] = None, heads_per_block: int = 0) -> None:
-    """Causal attention of each request's new tokens over its cached prefix and themselves.
+                      tile_rows: Optional[int] = None, heads_per_block: int = 0, softcap: Optional[float] = None,
+                      dv: Optional[int] = None) -> None:
+    """Causal attention of each request's new tokens over its cached prefix and themselves.  ``softcap``: scores
+    become softcap * tanh(score * scale / softcap) before the softmax (mma.sync and CUDA-core kernels); ``dv``: the
+    value head size where it differs from d (CUDA-core kernels; ``out`` is then [tokens, nq * dv]).
     ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)
     in steps of ``tile_rows`` (default: ``prefill_tile_rows(q.dtype, d)``), which also names the
     kernel: the tcgen05 kernel takes tiles of its own size, the others theirs.  ``heads_per_block``
@@ -482,19 +511,22 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
               _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"), _i32(tile_req, "tile_req"),
               _i32(tile_start, "tile_start"), tile_req.numel(), nq, nkv, d, page_size, int(window or 0), float(scale))
     lib = library()
-    base_rows = int(lib.lily_attention_prefill_mma_rows() if uses_tensor_cores(q.dtype, d) else lib.lily_attention_prefill_simt_rows())
+    dv = int(dv or d)
+    cap = float(softcap or 0.0)
+    tensor_cores = dv == d and uses_tensor_cores(q.dtype, d)
+    base_rows = int(lib.lily_attention_prefill_mma_rows() if tensor_cores else lib.lily_attention_prefill_simt_rows())
     if tile_rows is not None and tile_rows != base_rows:
-        if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16
+        if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16 and dv == d and not cap
                 and lib.lily_attention_prefill_tc_takes(int(d), int(page_size))):
             raise KernelError(f"attention_prefill: no kernel with tiles of {tile_rows} rows for {q.dtype}, head size {d}, "
                               f"page size {page_size}")
         if not (q.is_contiguous() and out.is_contiguous() and kv_layer.is_contiguous()):
             raise KernelError("attention_prefill: the tcgen05 kernel takes contiguous q, out and cache")
         _call("lily_attention_prefill_tc", *common, q.shape[0], kv_layer.shape[0], int(heads_per_block), _stream())
-    elif uses_tensor_cores(q.dtype, d):
-        _call("lily_attention_prefill_mma", *common, _stream())
+    elif tensor_cores:
+        _call("lily_attention_prefill_mma", *common, cap, _stream())
     else:
-        _call("lily_attention_prefill_simt", *common, _dt(q), _stream())
+        _call("lily_attention_prefill_simt", *common, _dt(q), cap, dv, _stream())
 
 
 def decode_clusters(d: int, splits: int, group: int) -> int:
@@ -509,7 +541,8 @@ def decode_scratch_floats(requests: int, nq: int, d: int, splits: int) -> int:
 
 def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
                      out: torch.Tensor, scratch: Optional[torch.Tensor], splits: int, nq: int, nkv: int, d: int,
-                     page_size: int, scale: float, window: Optional[int] = None, stages: int = 0) -> None:
+                     page_size: int, scale: float, window: Optional[int] = None, stages: int = 0,
+                     softcap: Optional[float] = None, dv: Optional[int] = None) -> None:
     """One query token per request (rows of ``q`` [requests, nq * d]) over ``seq_lens`` cached
     positions, keys cut into ``splits`` ranges merged through ``scratch`` (float32).  ``stages`` (tensor-core
     kernel only): the key/value tiles a block holds, 0 for the default (``DecodePlan.stages``)."""
@@ -517,20 +550,22 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     requests = q.shape[0]
     if q.dtype != kv_layer.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, cache and out must share a dtype")
-    need = decode_scratch_floats(requests, nq, d, splits)
+    dv = int(dv or d)
+    cap = float(softcap or 0.0)
+    need = decode_scratch_floats(requests, nq, dv, splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"attention_decode: scratch of {need} float32 needed")
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
               _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0),
               float(scale))
-    if uses_tensor_cores(q.dtype, d):
-        _call("lily_attention_decode_mma", *common, int(stages), _stream())   # merges the splits itself (cluster, or combine behind)
+    if dv == d and uses_tensor_cores(q.dtype, d):
+        _call("lily_attention_decode_mma", *common, int(stages), cap, _stream())   # merges the splits itself (cluster, or combine behind)
         if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
             launches["count"] += 1                                   # the combine kernel, launched inside
     else:
         if stages:
             raise KernelError(f"attention_decode: {stages} stages are the tensor-core kernel's; {q.dtype}, head size {d} runs on CUDA cores")
-        _call("lily_attention_decode_simt", *common, _dt(q), _stream())
+        _call("lily_attention_decode_simt", *common, _dt(q), cap, dv, _stream())
         if splits > 1:
             launches["count"] += 1          # the combine kernel, launched inside
 
@@ -610,7 +645,7 @@ def whole_rows_pay(pairs: int, sm_count: int = 148) -> bool:
 
 
 def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, d: int, max_seq_len: int,
-                          even: bool = False) -> DecodePlan:
+                          even: bool = False, dv: Optional[int] = None) -> DecodePlan:
     """The plan for ``requests`` rows that bring one token each, none longer than ``max_seq_len`` positions.
     A step in which every request brings one token may hand the qkv product straight to the attention kernel
     (``fused``): every block then finishes its own queries, which costs less than a kernel of its own while all
@@ -623,7 +658,8 @@ def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, 
     if requests == 0:
         return DecodePlan(1, False, 0, "single")
     group = nq // nkv
-    tensor_cores = uses_tensor_cores(dtype, d)
+    dv = int(dv or d)
+    tensor_cores = dv == d and uses_tensor_cores(dtype, d)      # values of another head size run on CUDA cores
     row_blocks = -(-group // 16)                 # the tensor-core kernel takes 16 query heads of a kv head a block
     pairs = requests * nkv * row_blocks
     if even and tensor_cores and d <= 128 and _WHOLE_ROWS and whole_rows_pay(pairs, sm_count()):
@@ -633,7 +669,7 @@ def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, 
     in_clusters = tensor_cores and splits > 1 and pairs <= decode_clusters(d, splits, group)
     fused = tensor_cores and pairs * splits <= 3 * sm_count()
     arm = "single" if splits == 1 else ("cluster" if in_clusters else "wave")
-    return DecodePlan(splits, fused, decode_scratch_floats(requests, nq, d, splits), arm)
+    return DecodePlan(splits, fused, decode_scratch_floats(requests, nq, dv, splits), arm)
 
 
 _WHOLE_ROWS = os.environ.get("LILY_B200_DECODE_WHOLE_ROWS", "1") != "0"
@@ -657,7 +693,7 @@ def attention_decode_fused(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_
                            block_table: torch.Tensor, seq_lens: torch.Tensor, out: torch.Tensor,
                            scratch: Optional[torch.Tensor], splits: int, nq: int, nkv: int, d: int, rotary_dim: int,
                            page_size: int, scale: float, window: Optional[int] = None, write_kv: bool = True,
-                           stages: int = 0) -> None:
+                           stages: int = 0, softcap: Optional[float] = None) -> None:
     """``qk_norm_rope_write`` and ``attention_decode`` of a step in which every request brings one token, as one
     kernel: ``qkv`` is the projection's result ([requests, (nq + 2 nkv) d] in the cache's dtype, or float32 partial
     sums [splits, requests, ...]); the attention blocks finish their own query heads, and the block whose key range
@@ -679,9 +715,130 @@ def attention_decode_fused(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_
     _call("lily_attention_decode_mma_fused", _p(qkv), planes, stride, _dt(qkv), _p(q_gain), _p(k_gain),
           _dt(q_gain) if q_gain is not None else _F32, float(eps), _p(cos), _p(sin), int(rotary_dim), int(write_kv),
           _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1], _i32(seq_lens, "seq_lens"),
-          _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0), float(scale), int(stages), _stream())
+          _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0), float(scale), int(stages),
+          float(softcap or 0.0), _stream())
     if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
         launches["count"] += 1                                       # the combine kernel, launched inside
+
+
+# ------------------------------------------------------------------------------ joining sublayers
+
+def _operand(t: torch.Tensor, rows: int, cols: int, what: str):
+    """(pointer, dtype code, splits, stride) of an input that is [rows, cols] in float32 or bfloat16, or float32
+    partial sums [splits, rows, cols]."""
+    splits, stride = _summed(t, rows, cols, what)
+    return _p(t), _dt(t), splits, stride
+
+
+def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """In place: ``out *= sigmoid(gate)``.  ``gate`` has ``out``'s shape [tokens, cols] (any of the two dtypes) or is
+    float32 partial sums [splits, tokens, cols]."""
+    _dev(out, gate)
+    n, cols = out.shape
+    ptr, dt, splits, stride = _operand(gate, n, cols, "sigmoid_gate")
+    _call("lily_sigmoid_gate", _p(out), _dt(out), ptr, dt, splits, stride, out.numel(), _stream())
+    return out
+
+
+def normed_mean(inputs: Sequence[torch.Tensor], gains: Sequence[torch.Tensor], eps: float,
+                add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``mean_k(rms(inputs[k]) * gains[k]) (+ add)`` row by row as float32 ``[1, tokens, width]`` (one plane of
+    partial sums, which the residual norm takes): rms(v) = v / sqrt(mean(v^2) + eps).  Inputs and ``add`` are
+    [tokens, width] or float32 partial sums [splits, tokens, width]; gains are float32 [width]."""
+    count = len(inputs)
+    lib = library()
+    if not 1 <= count <= int(lib.lily_normed_mean_max()) or len(gains) != count:
+        raise KernelError(f"normed_mean: {count} inputs with {len(gains)} gains")
+    _dev(*inputs, *gains, add)
+    n, width = inputs[0].shape[-2:]
+    ops_ = [_operand(t, n, width, "normed_mean input") for t in inputs]
+    for g in gains:
+        if g.dtype != torch.float32 or g.numel() != width:
+            raise KernelError("normed_mean: gains are float32 [width]")
+    a = _operand(add, n, width, "normed_mean add") if add is not None else (None, _F32, 1, 0)
+    out = torch.empty((1, n, width), dtype=torch.float32, device=inputs[0].device)
+    ptrs = (ctypes.c_void_p * count)(*[o[0] for o in ops_])
+    dts = (ctypes.c_int * count)(*[o[1] for o in ops_])
+    sps = (ctypes.c_int * count)(*[o[2] for o in ops_])
+    sts = (ctypes.c_size_t * count)(*[o[3] for o in ops_])
+    gs = (ctypes.c_void_p * count)(*[g.data_ptr() for g in gains])
+    _call("lily_normed_mean", ptrs, dts, sps, sts, gs, count, a[0], a[1], a[2], a[3], _p(out), n, width, float(eps),
+          1.0 / count, _stream())
+    return out
+
+
+# ------------------------------------------------------------------------------ state-space mixer
+
+SSM_CHUNK = 64          # new tokens a thread of the convolution kernel walks; a portion is cut at multiples of it
+
+
+def token_chunks(new_lens: Sequence[int], chunk: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(request, offset) of every run of up to ``chunk`` new tokens of every request, as two int32 device tensors."""
+    pairs = [(r, s) for r, n in enumerate(new_lens) for s in range(0, n, chunk)]
+    both = torch.tensor([[r for r, _ in pairs], [s for _, s in pairs]], dtype=torch.int32).reshape(2, -1)
+    both = both.to(device, non_blocking=True)
+    return both[0].contiguous(), both[1].contiguous()
+
+
+def causal_conv_silu(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                     state: torch.Tensor, state_off: int, chunk_req: torch.Tensor, chunk_start: torch.Tensor,
+                     cu_seqlens: torch.Tensor, slots: torch.Tensor, chunk: int = SSM_CHUNK) -> torch.Tensor:
+    """``silu(bias + causal depthwise convolution)`` over the columns ``[col0, col0 + channels)`` of ``proj``
+    [tokens, width], request by request: ``weight`` is float32 [channels, taps] whose last column multiplies the
+    current token; the ``taps - 1`` inputs before a portion's first token are read from, and its last ones written
+    to, ``state[slot, state_off:]`` (float32, [(taps - 1), channels], oldest first; zero for a new request)."""
+    _dev(proj, weight, bias, state, chunk_req, chunk_start, cu_seqlens, slots)
+    n, width = proj.shape
+    taps = weight.shape[1]
+    if weight.dtype != torch.float32 or tuple(weight.shape) != (channels, taps) or state.dtype != torch.float32:
+        raise KernelError("causal_conv_silu: float32 weights [channels, taps] and a float32 state")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != channels):
+        raise KernelError("causal_conv_silu: the bias is float32 [channels]")
+    if state.dim() != 2 or state_off + (taps - 1) * channels > state.shape[1] or col0 + channels > width:
+        raise KernelError("causal_conv_silu: columns or state out of range")
+    out = torch.empty((n, channels), dtype=proj.dtype, device=proj.device)
+    _call("lily_causal_conv_silu", _p(proj), width, int(col0), int(channels), int(taps), _p(weight), _p(bias), _p(state),
+          state.shape[1], int(state_off), _p(out), _i32(chunk_req, "chunk_req"), _i32(chunk_start, "chunk_start"),
+          chunk_req.numel(), int(chunk), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), _dt(proj), _stream())
+    return out
+
+
+def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+             d_skip: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, requests: int,
+             heads: int, head_dim: int, n_state: int, groups: int) -> torch.Tensor:
+    """The selective scan of each request's new tokens from its carried state, per head h of group g:
+    ``S = exp(-exp(a_log[h]) dt) S + dt B x^T``, ``y = S^T C + d_skip[h] x`` with ``dt = softplus(proj[:, dt_col + h] +
+    dt_bias[h])``, x = ``xbc[:, h * head_dim:]``, B and C = ``xbc[:, heads * head_dim + (g | groups + g) * n_state:]``.
+    ``state[slot, :heads * head_dim * n_state]`` holds S as [heads, head_dim, n_state] and is updated in place.
+    Returns y float32 [tokens, heads * head_dim]."""
+    _dev(xbc, proj, dt_bias, a_log, d_skip, state, cu_seqlens, slots)
+    n, channels = xbc.shape
+    inner = heads * head_dim
+    if channels != inner + 2 * groups * n_state or proj.dtype != xbc.dtype or proj.shape[0] != n:
+        raise KernelError(f"ssd_scan: xbc {tuple(xbc.shape)} {xbc.dtype} against proj {tuple(proj.shape)} {proj.dtype}")
+    for v in (dt_bias, a_log, d_skip):
+        if v.dtype != torch.float32 or v.numel() != heads:
+            raise KernelError("ssd_scan: dt_bias, a_log and d_skip are float32 [heads]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < inner * n_state or dt_col + heads > proj.shape[1]:
+        raise KernelError("ssd_scan: state or dt columns out of range")
+    y = torch.empty((n, inner), dtype=torch.float32, device=xbc.device)
+    _call("lily_ssd_scan", _p(xbc), channels, _p(proj), proj.shape[1], int(dt_col), _p(dt_bias), _p(a_log), _p(d_skip),
+          _p(state), state.shape[1], _p(y), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), int(requests), heads,
+          head_dim, n_state, groups, _dt(xbc), _stream())
+    return y
+
+
+def gated_group_rmsnorm(y: torch.Tensor, proj: torch.Tensor, gain: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
+    """``v = y * silu(z)`` with z the first ``y.shape[1]`` columns of ``proj``; each of ``groups`` equal runs of columns
+    divided by its own root mean square (eps inside the root), times ``gain`` (float32).  Returns ``proj``'s dtype."""
+    _dev(y, proj, gain)
+    n, inner = y.shape
+    if y.dtype != torch.float32 or gain.dtype != torch.float32 or gain.numel() != inner or proj.shape[0] != n or proj.shape[1] < inner:
+        raise KernelError("gated_group_rmsnorm: float32 y [tokens, inner] and gain [inner], proj [tokens, >= inner]")
+    out = torch.empty((n, inner), dtype=proj.dtype, device=y.device)
+    _call("lily_gated_group_rmsnorm", _p(y), _p(proj), proj.shape[1], _p(gain), _p(out), n, inner, int(groups), float(eps),
+          _dt(proj), _stream())
+    return out
 
 
 # ------------------------------------------------------------------------------ sampling

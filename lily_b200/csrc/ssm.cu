@@ -1,0 +1,265 @@
+// Kernels of the state-space mixer (Mamba-2 / state-space duality): the short causal convolution with its
+// carried inputs, the selective scan with its carried state, and the gated, grouped RMSNorm behind it.
+//
+// Everything that enters the recurrence is float32: the step size softplus(dt + bias), the decay
+// exp(-exp(A_log) * dt), the state and the sums over it.  Activations (`T`) are float or bfloat16.
+//
+// Per request the state lives in one float32 row of a slot table: first the scan state
+// [heads][head_dim][state] (state index fastest), then the last (taps - 1) inputs of the convolution
+// [(taps - 1)][channels], oldest first.  A request's row is zero when it starts.
+//
+//   conv:  u_t[c] = silu(bias[c] + sum_j w[c][j] * in_(t - (taps-1) + j)[c])        (inputs before the start are 0)
+//   scan:  S_t = exp(a * dt_t) S_(t-1) + dt_t * B_t x_t^T,   y_t = S_t^T C_t + D x_t     per head, a = -exp(A_log)
+//   norm:  v = y * silu(z);  out = v / sqrt(mean_over_group(v^2) + eps) * gain
+#include "common.cuh"
+
+namespace lily {
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// ---------------------------------------------------------------------------- causal convolution + SiLU
+
+// grid (ceil(channels / 128), chunks), block 128: a thread owns one channel of one chunk of up to `chunk_len`
+// consecutive new tokens of one request (chunks start at multiples of chunk_len >= taps - 1 from the portion's
+// first token, so only a portion's first chunk reads the carried inputs; the thread of that chunk also writes
+// them back, after it has read them, so no other thread touches what it reads).
+template <typename T, int TAPS>
+__global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride, int col0, int channels,
+                                        const float* __restrict__ w, const float* __restrict__ bias,
+                                        float* __restrict__ state, size_t state_stride, size_t state_off,
+                                        T* __restrict__ out, const int* __restrict__ chunk_req,
+                                        const int* __restrict__ chunk_start, int chunk_len,
+                                        const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
+    pdl_enter_small();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int r = chunk_req[blockIdx.y], start = chunk_start[blockIdx.y];
+    const int tok0 = cu_seqlens[r], len = cu_seqlens[r + 1] - tok0;
+    const int n = min(chunk_len, len - start);
+    if (n <= 0) return;
+    constexpr int K1 = TAPS - 1;
+    float* st = state + (size_t)slots[r] * state_stride + state_off + c;
+    const T* src = in + (size_t)tok0 * in_stride + col0 + c;
+    float win[K1 > 0 ? K1 : 1];
+    if (start == 0) {
+#pragma unroll
+        for (int j = 0; j < K1; ++j) win[j] = st[(size_t)j * channels];
+        if (len > chunk_len) {
+#pragma unroll
+            for (int j = 0; j < K1; ++j) st[(size_t)j * channels] = to_float(src[(size_t)(len - K1 + j) * in_stride]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < K1; ++j) win[j] = to_float(src[(size_t)(start - K1 + j) * in_stride]);
+    }
+    float wt[TAPS];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wt[j] = w[(size_t)c * TAPS + j];
+    const float b = bias ? bias[c] : 0.f;
+    T* dst = out + (size_t)(tok0 + start) * channels + c;
+    for (int t = 0; t < n; ++t) {
+        const float x = to_float(src[(size_t)(start + t) * in_stride]);
+        float acc = b;
+#pragma unroll
+        for (int j = 0; j < K1; ++j) acc = fmaf(win[j], wt[j], acc);
+        acc = fmaf(x, wt[K1], acc);
+#pragma unroll
+        for (int j = 0; j + 1 < K1; ++j) win[j] = win[j + 1];
+        if (K1 > 0) win[K1 - 1] = x;
+        dst[(size_t)t * channels] = from_float<T>(silu_f(acc));
+    }
+    if (start == 0 && len <= chunk_len) {
+#pragma unroll
+        for (int j = 0; j < K1; ++j) st[(size_t)j * channels] = win[j];
+    }
+}
+
+// ---------------------------------------------------------------------------- selective scan
+
+// grid (heads, requests, ceil(head_dim / pb)), block pb * ns threads: `ns` neighbouring lanes share one value
+// column p of the head's state and hold every ns-th of its `n_state` entries in registers (NPT each); the
+// tokens of the request run one after another, staged `tt` at a time in shared memory (B and C of the head's
+// group, the head's x, step sizes and decays).
+template <typename T, int NPT>
+__global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ proj, int proj_stride,
+                                int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                const float* __restrict__ d_skip, float* __restrict__ state, size_t state_stride,
+                                float* __restrict__ y, const int* __restrict__ cu_seqlens,
+                                const int* __restrict__ slots, int heads, int pd, int n_state, int groups, int ns,
+                                int pb, int tt) {
+    extern __shared__ float smem[];
+    pdl_enter_small();
+    const int h = blockIdx.x, r = blockIdx.y, p0 = blockIdx.z * pb;
+    const int tid = threadIdx.x, j = tid % ns, pl = tid / ns, p = p0 + pl;
+    const bool active = p < pd;
+    const int tok0 = cu_seqlens[r], len = cu_seqlens[r + 1] - tok0;
+    if (len <= 0) return;
+    float* Bs = smem;                        // [tt][n_state]
+    float* Cs = Bs + (size_t)tt * n_state;   // [tt][n_state]
+    float* xs = Cs + (size_t)tt * n_state;   // [tt][pb]
+    float* dts = xs + (size_t)tt * pb;       // [tt]
+    float* das = dts + tt;                   // [tt]
+    const int inner = heads * pd;
+    const int g = h / (heads / groups);
+    const int bcol = inner + g * n_state, ccol = inner + (groups + g) * n_state;
+    float* st = state + (size_t)slots[r] * state_stride + ((size_t)h * pd + (active ? p : 0)) * n_state;
+    float S[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = i * ns + j;
+        S[i] = (active && n < n_state) ? st[n] : 0.f;
+    }
+    const float A = -expf(a_log[h]), bias = dt_bias[h], D = d_skip[h];
+    for (int t0 = 0; t0 < len; t0 += tt) {
+        const int now = min(tt, len - t0);
+        __syncthreads();
+        for (int idx = tid; idx < now * n_state; idx += blockDim.x) {
+            const int ti = idx / n_state, n = idx - ti * n_state;
+            const T* row = xbc + (size_t)(tok0 + t0 + ti) * channels;
+            Bs[ti * n_state + n] = to_float(row[bcol + n]);
+            Cs[ti * n_state + n] = to_float(row[ccol + n]);
+        }
+        for (int idx = tid; idx < now * pb; idx += blockDim.x) {
+            const int ti = idx / pb, q = idx - ti * pb;
+            xs[ti * pb + q] = p0 + q < pd ? to_float(xbc[(size_t)(tok0 + t0 + ti) * channels + h * pd + p0 + q]) : 0.f;
+        }
+        if (tid < now) {
+            const float dtv = softplus_f(to_float(proj[(size_t)(tok0 + t0 + tid) * proj_stride + dt_col + h]) + bias);
+            dts[tid] = dtv;
+            das[tid] = expf(A * dtv);
+        }
+        __syncthreads();
+        for (int ti = 0; ti < now; ++ti) {
+            const float xv = xs[ti * pb + pl], da = das[ti], coef = dts[ti] * xv;
+            const float* bt = Bs + ti * n_state;
+            const float* ct = Cs + ti * n_state;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+                const int n = i * ns + j;
+                if (n < n_state) {
+                    S[i] = fmaf(da, S[i], coef * bt[n]);
+                    acc = fmaf(S[i], ct[n], acc);
+                }
+            }
+            for (int o = ns >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (j == 0 && active) y[(size_t)(tok0 + t0 + ti) * inner + h * pd + p] = fmaf(D, xv, acc);
+        }
+    }
+    if (active) {
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int n = i * ns + j;
+            if (n < n_state) st[n] = S[i];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------- gate, then grouped RMSNorm
+
+// grid (tokens, groups), block 256: v = y * silu(z) over one group of `gsize` columns, normalised by the
+// group's own root mean square, times the gain.
+template <typename T>
+__global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ z, int z_stride,
+                                           const float* __restrict__ gain, T* __restrict__ out, int inner,
+                                           int gsize, float eps) {
+    __shared__ float red[33];
+    pdl_enter_small();
+    const size_t t = blockIdx.x;
+    const int c0 = blockIdx.y * gsize;
+    const float* yr = y + t * inner + c0;
+    const T* zr = z + t * z_stride + c0;
+    float ssq = 0.f;
+    for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
+        const float v = yr[i] * silu_f(to_float(zr[i]));
+        ssq = fmaf(v, v, ssq);
+    }
+    const float inv = rsqrtf(block_sum(ssq, red) / (float)gsize + eps);
+    T* dst = out + t * inner + c0;
+    for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
+        const float v = yr[i] * silu_f(to_float(zr[i]));
+        dst[i] = from_float<T>((v * inv) * gain[c0 + i]);
+    }
+}
+
+}  // namespace lily
+
+using namespace lily;
+
+LILY_API int lily_conv_max_taps() { return 8; }
+
+LILY_API int lily_causal_conv_silu(const void* in, int in_stride, int col0, int channels, int taps, const float* w,
+                                   const float* bias, float* state, size_t state_stride, size_t state_off, void* out,
+                                   const int* chunk_req, const int* chunk_start, int chunks, int chunk_len,
+                                   const int* cu_seqlens, const int* slots, int dtype, cudaStream_t stream) {
+    if (chunks == 0 || channels == 0) return 0;
+    LILY_REQUIRE(taps >= 1 && taps <= 8, "causal_conv_silu: %d taps (1 to 8)", taps);
+    LILY_REQUIRE(chunk_len >= taps - 1 && chunk_len >= 1, "causal_conv_silu: chunks of %d tokens for %d taps", chunk_len, taps);
+    LILY_REQUIRE(chunks <= 65535, "causal_conv_silu: %d chunks", chunks);
+    dim3 grid((channels + 127) / 128, chunks), block(128);
+#define GO(T, K)                                                                                                     \
+    launch_pdl(causal_conv_silu_kernel<T, K>, grid, block, 0, stream, (const T*)in, in_stride, col0, channels, w, bias, \
+               state, state_stride, state_off, (T*)out, chunk_req, chunk_start, chunk_len, cu_seqlens, slots)
+#define TAPS_CASE(K) case K: if (dtype == kBF16) GO(__nv_bfloat16, K); else GO(float, K); break;
+    switch (taps) {
+        TAPS_CASE(1) TAPS_CASE(2) TAPS_CASE(3) TAPS_CASE(4) TAPS_CASE(5) TAPS_CASE(6) TAPS_CASE(7) TAPS_CASE(8)
+    }
+#undef TAPS_CASE
+#undef GO
+    LILY_CHECK_LAUNCH("causal_conv_silu");
+    return 0;
+}
+
+LILY_API int lily_ssd_scan_max_state() { return 512; }
+
+LILY_API int lily_ssd_scan(const void* xbc, int channels, const void* proj, int proj_stride, int dt_col,
+                           const float* dt_bias, const float* a_log, const float* d_skip, float* state,
+                           size_t state_stride, float* y, const int* cu_seqlens, const int* slots, int requests,
+                           int heads, int pd, int n_state, int groups, int dtype, cudaStream_t stream) {
+    if (requests == 0) return 0;
+    LILY_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0, "ssd_scan: %d heads over %d groups", heads, groups);
+    LILY_REQUIRE(n_state >= 1 && n_state <= 512 && pd >= 1, "ssd_scan: state %d (1 to 512), head size %d", n_state, pd);
+    LILY_REQUIRE(requests <= 65535, "ssd_scan: %d requests", requests);
+    // ns lanes share a value column, each with npt = 4, 8 or 16 entries of its state
+    int npt = n_state <= 32 ? 4 : (n_state <= 128 ? 8 : 16);
+    int ns = 1;
+    while (ns * npt < n_state) ns <<= 1;
+    if (ns > 32) { ns = 32; npt = 16; }
+    int pb = 256 / ns;                                   // value columns a block
+    while (pb > 32 / ns && pb / 2 >= pd) pb >>= 1;       // no wider than the head, but whole warps
+    if (pb < 32 / ns) pb = 32 / ns;
+    if (pb < 1) pb = 1;
+    int tt = 16;
+    while (tt > 1 && (size_t)tt * (2 * n_state + pb + 2) * sizeof(float) > 40 * 1024) tt >>= 1;
+    const size_t smem = (size_t)tt * (2 * n_state + pb + 2) * sizeof(float);
+    dim3 grid(heads, requests, (pd + pb - 1) / pb), block(pb * ns);
+#define GO(T, N)                                                                                                       \
+    launch_pdl(ssd_scan_kernel<T, N>, grid, block, smem, stream, (const T*)xbc, channels, (const T*)proj, proj_stride,  \
+               dt_col, dt_bias, a_log, d_skip, state, state_stride, y, cu_seqlens, slots, heads, pd, n_state, groups, ns, \
+               pb, tt)
+    if (dtype == kBF16) {
+        if (npt == 4) GO(__nv_bfloat16, 4); else if (npt == 8) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 16);
+    } else {
+        if (npt == 4) GO(float, 4); else if (npt == 8) GO(float, 8); else GO(float, 16);
+    }
+#undef GO
+    LILY_CHECK_LAUNCH("ssd_scan");
+    return 0;
+}
+
+LILY_API int lily_gated_group_rmsnorm(const float* y, const void* z, int z_stride, const float* gain, void* out,
+                                      int tokens, int inner, int groups, float eps, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LILY_REQUIRE(groups >= 1 && inner % groups == 0, "gated_group_rmsnorm: %d columns in %d groups", inner, groups);
+    LILY_REQUIRE(groups <= 65535, "gated_group_rmsnorm: %d groups", groups);
+    dim3 grid(tokens, groups), block(256);
+    if (dtype == kBF16)
+        launch_pdl(gated_group_rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, stream, y, (const __nv_bfloat16*)z, z_stride,
+                   gain, (__nv_bfloat16*)out, inner, inner / groups, eps);
+    else
+        launch_pdl(gated_group_rmsnorm_kernel<float>, grid, block, 0, stream, y, (const float*)z, z_stride, gain,
+                   (float*)out, inner, inner / groups, eps);
+    LILY_CHECK_LAUNCH("gated_group_rmsnorm");
+    return 0;
+}

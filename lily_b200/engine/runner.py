@@ -22,7 +22,7 @@ import torch
 
 from lily_b200.cache.kv_cache import KVCacheManager, OutOfPages, bytes_per_token, pool_pages_from_memory
 from lily_b200.config.model_config import read_model_dir
-from lily_b200.config.registry import resolve_architecture
+from lily_b200.config.registry import architecture_names, resolve_architecture
 from lily_b200.config.server_args import ServerArgs
 from lily_b200.engine import check
 from lily_b200.engine.batch import FUTURE, StepBatch, StepEntry, Workspace, build_step_batch, order_entries, rows_are_even
@@ -232,7 +232,7 @@ class ModelRunner:
     @classmethod
     def from_model_dir(cls, args: ServerArgs, ops: Any = None) -> "ModelRunner":
         cfg, gen = read_model_dir(args.model_path)
-        arch = resolve_architecture(cfg.get("architectures"))
+        arch = resolve_architecture(architecture_names(cfg))
         config = arch.config_from_dict(cfg, gen, architecture=arch.name)
         return cls(arch.build_spec(config), CheckpointSource(args.model_path), args, ops)
 
@@ -242,7 +242,7 @@ class ModelRunner:
         """A model with seeded random weights drawn on the device, without a file."""
         from lily_b200.weights.random_init import RandomSource, expected_tensors
 
-        arch = resolve_architecture(config_json.get("architectures"))
+        arch = resolve_architecture(architecture_names(config_json))
         config = arch.config_from_dict(config_json, {}, architecture=arch.name)
         store = torch.float32 if args.dtype == "float32" else torch.bfloat16
         source = RandomSource(expected_tensors(config, arch), seed, store, args.device, std, gain_jitter)

@@ -57,7 +57,7 @@ class AssembledModel:
                         raise ValueError(f"schedule position {pos} reads the cache of position {entry.reads}, "
                                          f"whose mixer {k} has none")
                     other = owners[k].cache_need()
-                    if (other.kv_heads, other.head_dim) != (need.kv_heads, need.head_dim):
+                    if (other.kv_heads, other.head_dim, other.v_head_dim) != (need.kv_heads, need.head_dim, need.v_head_dim):
                         raise ValueError(f"schedule position {pos} cannot read a cache of another shape")
                     if other.window is not None and (need.window is None or need.window > other.window):
                         # the owner's group gives pages back once its window has passed them

@@ -4,7 +4,10 @@ q, k and v come from one product with the stacked matrix ``[q rows | k rows | v 
 kernel then normalises each q and k head (when ``qk_norm``), rotates them by the position tables,
 leaves q in a buffer and writes k and v into the token's page; attention runs over the cache
 (split-key decode kernel for requests that bring one token, prefill kernel for portions); the
-output projection closes the part.  How a step's attention is cut (key ranges, kernel forms, tile
+output projection closes the part.  Options of the spec: a value head size of its own (``v_head_dim``), scores soft-capped
+to ``softcap * tanh(score / softcap)``, an output gate (the concatenated heads times ``sigmoid(W_g x)`` ahead of the
+output projection, W_g reading the mixer's input), rotation of interleaved pairs (the rows of the q and k projections
+are reordered once at load time, see ``rope.pairing_order``), and the checkpoint's own tensor names.  How a step's attention is cut (key ranges, kernel forms, tile
 lists) is this part's own plan, made once a step from the batch's host fields by asking the kernels
 (``ops.plan_decode_attention``, ``ops.prefill_tile_rows``, ``ops.prefill_tiles``); the step function
 knows nothing of it.  Sizes, eps, scale, window and the position encoding are
@@ -18,7 +21,7 @@ lily/layers/attention/triton_backend.py:110-141 (cache write before attention).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Dict, Optional
+from typing import Any, Dict, Optional, Tuple
 
 import torch
 
@@ -38,6 +41,18 @@ class AttentionSpec:
     scale: Optional[float] = None         # None: head_dim ** -0.5
     position: Any = None                  # a position spec (e.g. RopeSpec) or None
     kind: str = "attention"
+    v_head_dim: Optional[int] = None      # None: head_dim
+    softcap: Optional[float] = None       # scores become softcap * tanh(score * scale / softcap)
+    out_gate: bool = False                # heads * sigmoid(W_g x) before the output projection
+    # names of the tensors under the part's prefix: q, k, v, o (and g) weights; None: "<x>_proj.weight"
+    names: Optional[Tuple[Tuple[str, str], ...]] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
+
+    def name(self, role: str) -> str:
+        return dict(self.names or ()).get(role, f"{role}_proj.weight")
 
 
 @dataclass
@@ -55,7 +70,8 @@ class LayerCache:
     """The cache one run of a mixer reads and writes: its group and its layer's pages."""
 
     group: int
-    data: torch.Tensor            # [pages + 1, 2, kv_heads, page_size, head_dim]
+    data: torch.Tensor            # [pages + 1, 2, kv_heads, page_size, head_dim], or flat pages when values have a
+                                  # head size of their own (``ops.cache_layer_fits``)
 
 
 @register_part("mixer", "attention")
@@ -68,20 +84,26 @@ class Attention(Mixer):
         self.spec, self.prefix, self.ctx = spec, prefix, ctx
         self.scale = spec.scale if spec.scale is not None else spec.head_dim ** -0.5
         self.position = build_part("position", spec.position, prefix, ctx) if spec.position is not None else None
-        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_gain = self.k_gain = None
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_gain = self.k_gain = self.w_g = None
+        if spec.value_dim != spec.head_dim and (spec.bias or spec.qk_norm):
+            raise ValueError("a value head size of its own comes without biases and q/k norms")
 
     # ---- what it needs ----------------------------------------------------------
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+        s = self.spec
+        return CacheNeed(s.num_kv_heads, s.head_dim, s.window, None if s.value_dim == s.head_dim else s.value_dim)
 
     def tensors(self) -> Dict[str, TensorSpec]:
         s, p = self.spec, self.prefix
         q, kv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
-        out = {f"{p}.q_proj.weight": TensorSpec((q, s.hidden_size)),
-               f"{p}.k_proj.weight": TensorSpec((kv, s.hidden_size)),
-               f"{p}.v_proj.weight": TensorSpec((kv, s.hidden_size)),
-               f"{p}.o_proj.weight": TensorSpec((s.hidden_size, q))}
+        heads_out = s.num_heads * s.value_dim
+        out = {f"{p}.{s.name('q')}": TensorSpec((q, s.hidden_size)),
+               f"{p}.{s.name('k')}": TensorSpec((kv, s.hidden_size)),
+               f"{p}.{s.name('v')}": TensorSpec((s.num_kv_heads * s.value_dim, s.hidden_size)),
+               f"{p}.{s.name('o')}": TensorSpec((s.hidden_size, heads_out))}
+        if s.out_gate:
+            out[f"{p}.{s.name('g')}"] = TensorSpec((heads_out, s.hidden_size))
         if s.bias:
             out.update({f"{p}.q_proj.bias": TensorSpec((q,), role="matrix"),
                         f"{p}.k_proj.bias": TensorSpec((kv,), role="matrix"),
@@ -95,13 +117,21 @@ class Attention(Mixer):
     def load(self, get) -> None:
         s, p = self.spec, self.prefix
         q, kv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
-        wq = get(f"{p}.q_proj.weight")
-        self.w_qkv = torch.empty((q + 2 * kv, s.hidden_size), dtype=wq.dtype, device=wq.device)
+        wq, wk = get(f"{p}.{s.name('q')}"), get(f"{p}.{s.name('k')}")
+        if self.position is not None and getattr(self.position, "interleaved", False):
+            # pairs (2i, 2i + 1) become (i, i + rotary_dim / 2) in every q and k head alike: the scores are the same
+            from lily_b200.parts.rope import pairing_order
+            order = pairing_order(s.head_dim, self.position.rotary_dim).to(wq.device)
+            wq = wq.view(s.num_heads, s.head_dim, -1)[:, order].reshape(q, -1)
+            wk = wk.view(s.num_kv_heads, s.head_dim, -1)[:, order].reshape(kv, -1)
+        self.w_qkv = torch.empty((q + kv + s.num_kv_heads * s.value_dim, s.hidden_size), dtype=wq.dtype, device=wq.device)
         self.w_qkv[:q].copy_(wq)
-        del wq
-        self.w_qkv[q:q + kv].copy_(get(f"{p}.k_proj.weight"))
-        self.w_qkv[q + kv:].copy_(get(f"{p}.v_proj.weight"))
-        self.w_o = get(f"{p}.o_proj.weight").contiguous()
+        self.w_qkv[q:q + kv].copy_(wk)
+        del wq, wk
+        self.w_qkv[q + kv:].copy_(get(f"{p}.{s.name('v')}"))
+        self.w_o = get(f"{p}.{s.name('o')}").contiguous()
+        if s.out_gate:
+            self.w_g = get(f"{p}.{s.name('g')}").contiguous()
         if s.bias:
             self.b_qkv = torch.cat([get(f"{p}.{n}_proj.bias") for n in "qkv"]).contiguous()
             self.b_o = get(f"{p}.o_proj.bias").contiguous()
@@ -117,25 +147,27 @@ class Attention(Mixer):
         """How this step's attention runs for this mixer's sizes in cache group ``group``; made once a step and
         shared by every layer with the same sizes (``batch.plan``)."""
         s, ops = self.spec, self.ctx.ops
-        key = ("attention", group, s.num_heads, s.num_kv_heads, s.head_dim, dtype, page)
+        key = ("attention", group, s.num_heads, s.num_kv_heads, s.head_dim, dtype, page, s.value_dim, bool(s.softcap))
+        dv = s.value_dim
 
         def make(b):
             nd = b.num_decode
             decode = ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
-                                               even=b.decode_even)
+                                               even=b.decode_even, dv=dv)
             if decode != ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
-                                                   even=not b.decode_even):
+                                                   even=not b.decode_even, dv=dv):
                 b.even_asked = True              # a captured step with this plan serves batches of this kind only
             rows = tiles = None
             if b.num_requests > nd:
-                rows = ops.prefill_tile_rows(dtype, s.head_dim, page, b.num_tokens - nd)
+                rows = ops.prefill_tile_rows(dtype, s.head_dim, page, b.num_tokens - nd, softcap=s.softcap, dv=dv)
                 tiles = ops.prefill_tiles(b.h_prefix_lens, b.h_new_lens, nd, rows, b.token_ids.device)
             return AttentionPlan(decode, rows, tiles)
         return batch.plan(key, make)
 
     def forward(self, x, batch, cache: LayerCache, state=None, write_cache: bool = True):
         s, ops = self.spec, self.ctx.ops
-        page = cache.data.shape[3]
+        page = self.ctx.page_size
+        dv = s.value_dim
         table = batch.block_tables[cache.group]
         plan = self._plan(batch, cache.group, cache.data.dtype, page)
         qkv = ops.linear_auto(x, self.w_qkv, self.b_qkv)
@@ -143,23 +175,29 @@ class Attention(Mixer):
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         nd, dec = batch.num_decode, plan.decode
         scratch = batch.workspace.floats("attention_decode", dec.scratch_floats) if nd and dec.scratch_floats else None
+        gate = ops.linear_auto(x, self.w_g) if s.out_gate else None
         if nd == batch.num_tokens and dec.fused:
             # every request brings one token: the decode attention kernel finishes q, k and v itself
             out = torch.empty((nd, s.num_heads * s.head_dim), dtype=cache.data.dtype, device=cache.data.device)
             ops.attention_decode_fused(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, cache.data, table, batch.seq_lens,
                                        out, scratch, dec.splits, s.num_heads, s.num_kv_heads, s.head_dim, rotary_dim, page,
-                                       self.scale, s.window, write_kv=write_cache, stages=dec.stages)
+                                       self.scale, s.window, write_kv=write_cache, stages=dec.stages, softcap=s.softcap)
+            if gate is not None:
+                ops.sigmoid_gate(out, gate)
             return ops.linear_auto(out, self.w_o, self.b_o)
         q = ops.qk_norm_rope_write(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, batch.positions,
                                    batch.token_req, table, cache.data, s.num_heads, s.num_kv_heads, s.head_dim,
-                                   rotary_dim, page, write_kv=write_cache)
-        out = torch.empty_like(q)       # [tokens, heads * head_dim]
+                                   rotary_dim, page, write_kv=write_cache, dv=dv)
+        out = torch.empty((q.shape[0], s.num_heads * dv), dtype=q.dtype, device=q.device)
         if nd:
             ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, dec.splits,
-                                 s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window, stages=dec.stages)
+                                 s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window, stages=dec.stages,
+                                 softcap=s.softcap, dv=dv)
         if batch.num_requests > nd:
             tile_req, tile_start = plan.tiles
             ops.attention_prefill(q, cache.data, table, batch.cu_seqlens, batch.prefix_lens, tile_req, tile_start,
                                   out, s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window,
-                                  tile_rows=plan.tile_rows)
+                                  tile_rows=plan.tile_rows, softcap=s.softcap, dv=dv)
+        if gate is not None:
+            ops.sigmoid_gate(out, gate)
         return ops.linear_auto(out, self.w_o, self.b_o)

@@ -73,6 +73,7 @@ class CacheNeed:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None     # the values' head size where it differs from the keys' (None: head_dim)
 
 
 @dataclass(frozen=True)
@@ -196,7 +197,7 @@ def _load_builtin_parts() -> None:
     global _BUILTINS
     if not _BUILTINS:
         _BUILTINS = True
-        from lily_b200.parts import attention, block, mlp, norm, rope  # noqa: F401
+        from lily_b200.parts import attention, block, mlp, norm, rope, ssm  # noqa: F401
 
 
 # --------------------------------------------------------------------------- model description

@@ -1,4 +1,5 @@
-"""The pre-norm block: ``r += mixer(norm_in(r)); r += feed_forward(norm_post(r))``.
+"""Block arrangements.  The pre-norm block: ``r += mixer(norm_in(r)); r += feed_forward(norm_post(r))``; the parallel
+block (``ParallelBlockSpec``): one norm, several mixers and the feed-forward side by side on its output.
 
 The residual stream ``r`` is float32 and updated in place; each add is fused into the norm that
 follows it, so a block receives the pending delta of the block before it and returns its own
@@ -7,7 +8,8 @@ follows it, so a block receives the pending delta of the block before it and ret
 
 from __future__ import annotations
 
-from typing import Dict
+from dataclasses import dataclass
+from typing import Any, Dict, Tuple
 
 from lily_b200.parts.base import Block, BlockSpec, BuildContext, RunSlots, TensorSpec, build_part, register_part
 
@@ -39,3 +41,57 @@ class PreNormBlock(Block):
         a = self.mixer.forward(x, batch, run.caches[0], run.states[0], run.write_cache)
         y = self.norm_post.forward(residual, a)
         return self.feed_forward.forward(y, batch)
+
+
+@dataclass(frozen=True)
+class ParallelBlockSpec:
+    """One norm whose output every sublayer reads: ``h = norm(r)``, ``r += mean_k(rms(mixer_k(h)) * gain_k) + ff(h)``.
+    ``mixers`` lists (name under the block's prefix, mixer spec, name of the mixer's output gain); the feed-forward
+    may be absent.  The mixers run side by side on the same ``h``; each output is divided by its root mean square
+    over the model width (``eps``) and multiplied by its own gain before the mean is taken."""
+
+    prefix: str
+    hidden_size: int
+    mixers: Tuple[Tuple[str, Any, str], ...]
+    feed_forward: Any
+    norm: Any
+    eps: float
+    kind: str = "parallel"
+    norm_name: str = "norm1"
+    feed_forward_name: str = "mlp"
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Block):
+    def __init__(self, spec: ParallelBlockSpec, prefix: str, ctx: BuildContext):
+        if not spec.mixers:
+            raise ValueError("a parallel block has at least one mixer")
+        self.spec, self.ctx = spec, ctx
+        p = spec.prefix
+        self.norm = build_part("norm", spec.norm, f"{p}.{spec.norm_name}", ctx)
+        self.mixers = tuple(build_part("mixer", m, f"{p}.{name}", ctx) for name, m, _ in spec.mixers)
+        self.feed_forward = None if spec.feed_forward is None else \
+            build_part("feed_forward", spec.feed_forward, f"{p}.{spec.feed_forward_name}", ctx)
+        self.parts = (self.norm, *self.mixers) + ((self.feed_forward,) if self.feed_forward is not None else ())
+        self.gain_names = [f"{p}.{gain}" for _, _, gain in spec.mixers]
+        self.gains = []
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        out: Dict[str, TensorSpec] = {}
+        for part in self.parts:
+            out.update(part.tensors())
+        for name in self.gain_names:
+            out[name] = TensorSpec((self.spec.hidden_size,), role="vector", init="gain")
+        return out
+
+    def load(self, get) -> None:
+        for part in self.parts:
+            part.load(get)
+        self.gains = [get(name).float().contiguous() for name in self.gain_names]
+
+    def forward(self, residual, delta, batch, run: RunSlots):
+        h = self.norm.forward(residual, delta)
+        outs = [m.forward(h, batch, run.caches[k], run.states[k], run.write_cache) for k, m in enumerate(self.mixers)]
+        f = self.feed_forward.forward(h, batch) if self.feed_forward is not None else None
+        # float32, as one plane of partial sums: the next norm adds it into the residual stream
+        return self.ctx.ops.normed_mean(outs, self.gains, self.spec.eps, add=f)

@@ -1,4 +1,5 @@
-"""Dense SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))``, no bias.
+"""Dense gated feed-forward: ``down(act(gate(x)) * up(x))``, no bias; act is SiLU (SwiGLU) unless the spec names
+another (``"gelu_tanh"``: the product and the activation kernel then run separately).
 
 gate and up are one matrix ``[2 * inter, hidden]`` so that one product feeds the SiLU*mul
 (lily/models/llama.py:31-47, stacking llama.py:164-165).  In bfloat16, when the intermediate size
@@ -13,7 +14,7 @@ reference streams these products through its own kernel as well (lily/csrc/bf16_
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -25,6 +26,12 @@ class SwiGLUSpec:
     hidden_size: int
     intermediate_size: int
     kind: str = "swiglu"
+    activation: str = "silu"              # "silu" | "gelu_tanh"
+    # names of the gate, up and down weights under the part's prefix; None: "<x>_proj.weight"
+    names: Optional[Tuple[Tuple[str, str], ...]] = None
+
+    def name(self, role: str) -> str:
+        return dict(self.names or ()).get(role, f"{role}_proj.weight")
 
 
 @register_part("feed_forward", "swiglu")
@@ -37,12 +44,14 @@ class SwiGLU(FeedForward):
 
     def tensors(self) -> Dict[str, TensorSpec]:
         h, i, p = self.spec.hidden_size, self.spec.intermediate_size, self.prefix
-        return {f"{p}.gate_proj.weight": TensorSpec((i, h)), f"{p}.up_proj.weight": TensorSpec((i, h)),
-                f"{p}.down_proj.weight": TensorSpec((h, i))}
+        n = self.spec.name
+        return {f"{p}.{n('gate')}": TensorSpec((i, h)), f"{p}.{n('up')}": TensorSpec((i, h)),
+                f"{p}.{n('down')}": TensorSpec((h, i))}
 
     def load(self, get) -> None:
         p, i = self.prefix, self.spec.intermediate_size
-        gate = get(f"{p}.gate_proj.weight")
+        name = self.spec.name
+        gate = get(f"{p}.{name('gate')}")
         h = self.spec.hidden_size
         self.w_gate_up = torch.empty((2 * i, h), dtype=gate.dtype, device=gate.device)
         self.block = b = self.ctx.ops.gate_up_interleave(gate.dtype, i)
@@ -50,16 +59,19 @@ class SwiGLU(FeedForward):
             runs = self.w_gate_up.view(i // b, 2, b, h)
             runs[:, 0].copy_(gate.view(i // b, b, h))
             del gate
-            runs[:, 1].copy_(get(f"{p}.up_proj.weight").view(i // b, b, h))
+            runs[:, 1].copy_(get(f"{p}.{name('up')}").view(i // b, b, h))
         else:
             self.w_gate_up[:i].copy_(gate)
             del gate
-            self.w_gate_up[i:].copy_(get(f"{p}.up_proj.weight"))
-        self.w_down = get(f"{p}.down_proj.weight").contiguous()
+            self.w_gate_up[i:].copy_(get(f"{p}.{name('up')}"))
+        self.w_down = get(f"{p}.{name('down')}").contiguous()
 
     def forward(self, x, batch):
         ops = self.ctx.ops
         product = ops.linear_auto                                # partial sums for a few tokens, else [M, N]
+        if self.spec.activation != "silu":
+            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, block=self.block, activation=self.spec.activation)
+            return product(act, self.w_down)
         few = ops.swiglu_skinny_need(x.shape[0], self.spec.intermediate_size, self.spec.hidden_size, x.dtype, self.block)
         if few is not None and batch.workspace is not None:
             # a few tokens: one kernel streams the fused matrix and applies SiLU*mul to its own sums

@@ -19,6 +19,7 @@ class RMSNormSpec:
     size: int
     eps: float
     kind: str = "rmsnorm"
+    suffix: str = ".weight"        # the gain's name is the part's prefix followed by this ("" where the prefix is the name)
 
 
 @register_part("norm", "rmsnorm")
@@ -28,10 +29,10 @@ class RMSNorm(Norm):
         self.weight = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {f"{self.prefix}.weight": TensorSpec((self.spec.size,), role="vector", init="gain")}
+        return {f"{self.prefix}{self.spec.suffix}": TensorSpec((self.spec.size,), role="vector", init="gain")}
 
     def load(self, get) -> None:
-        self.weight = get(f"{self.prefix}.weight")
+        self.weight = get(f"{self.prefix}{self.spec.suffix}")
 
     def forward(self, residual, delta=None, delta_bias=None, rows=None, write_residual=True):
         if delta_bias is not None:

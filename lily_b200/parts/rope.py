@@ -28,10 +28,24 @@ class RopeSpec:
     theta: float
     scaling: RopeScaling = field(default_factory=RopeScaling)
     kind: str = "rope"
+    # True: feature 2i is paired with feature 2i + 1 (the interleaved layout) instead of i with i + rotary_dim / 2.
+    # A score q . k does not change when the features of q and k are reordered alike, so a mixer serves this layout
+    # by reordering the rows of its q and k projections once, when it loads them (``pairing_order``), and the kernels
+    # rotate halves as ever.
+    interleaved: bool = False
+    # True: the frequencies are worked out in float64 and then rounded to float32 (a float32 power is up to a few
+    # units in the last place off, which a position of a thousand turns into 1e-4 of a radian); the angles are
+    # float32 products either way
+    exact_frequencies: bool = False
 
 
 def inverse_frequencies(spec: RopeSpec) -> torch.Tensor:
-    inv = 1.0 / (spec.theta ** (torch.arange(0, spec.rotary_dim, 2, dtype=torch.float32) / spec.rotary_dim))
+    work = torch.float64 if spec.exact_frequencies else torch.float32
+    inv = 1.0 / (spec.theta ** (torch.arange(0, spec.rotary_dim, 2, dtype=work) / spec.rotary_dim))
+    return _scaled(inv, spec).to(torch.float32)
+
+
+def _scaled(inv: torch.Tensor, spec: RopeSpec) -> torch.Tensor:
     s = spec.scaling
     if s.rope_type == "default":
         return inv
@@ -49,15 +63,29 @@ def inverse_frequencies(spec: RopeSpec) -> torch.Tensor:
     return torch.where(wavelen < high_wavelen, inv, torch.where(wavelen > low_wavelen, inv / s.factor, mid))
 
 
+def pairing_order(head_dim: int, rotary_dim: int) -> torch.Tensor:
+    """For each feature of a head in the order the kernels rotate (first halves, second halves, the rest), the
+    feature of the interleaved layout that stands there: [0, 2, 4, ..., 1, 3, 5, ..., rotary_dim, ...]."""
+    return torch.cat([torch.arange(0, rotary_dim, 2), torch.arange(1, rotary_dim, 2), torch.arange(rotary_dim, head_dim)])
+
+
+_TABLES = {}      # (spec, positions, device) -> (cos, sin): layers with the same encoding share one pair of tables
+
+
 @register_part("position", "rope")
 class RotaryTable(Part):
     def __init__(self, spec: RopeSpec, prefix: str, ctx: BuildContext):
         self.spec, self.ctx = spec, ctx
         self.rotary_dim = spec.rotary_dim
-        t = torch.arange(ctx.max_position, dtype=torch.float32)
-        freqs = torch.outer(t, inverse_frequencies(spec))          # float32 on the host
-        self._cos = freqs.cos().contiguous().to(ctx.device)
-        self._sin = freqs.sin().contiguous().to(ctx.device)
+        self.interleaved = spec.interleaved
+        key = (spec.rotary_dim, spec.theta, spec.scaling, spec.exact_frequencies, ctx.max_position, str(ctx.device))
+        if key not in _TABLES:
+            if len(_TABLES) > 16:
+                _TABLES.clear()
+            t = torch.arange(ctx.max_position, dtype=torch.float32)
+            freqs = torch.outer(t, inverse_frequencies(spec))          # float32 on the host
+            _TABLES[key] = (freqs.cos().contiguous().to(ctx.device), freqs.sin().contiguous().to(ctx.device))
+        self._cos, self._sin = _TABLES[key]
 
     def tables(self):
         return self._cos, self._sin

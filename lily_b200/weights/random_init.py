@@ -73,9 +73,9 @@ def write_random_model(path: str, config_json: Dict[str, Any], seed: int, dtype:
     """Writes ``path/config.json`` and ``path/model.safetensors`` for the architecture that
     ``config_json["architectures"]`` names.  ``dtype`` ("bfloat16" | "float32") defaults to the
     configuration's ``torch_dtype``."""
-    from lily_b200.config.registry import resolve_architecture
+    from lily_b200.config.registry import architecture_names, resolve_architecture
 
-    arch = resolve_architecture(config_json.get("architectures"))
+    arch = resolve_architecture(architecture_names(config_json))
     config = arch.config_from_dict(config_json, {}, architecture=arch.name)
     store = dtype or config_json.get("torch_dtype") or "bfloat16"
     if store not in _DTYPES:

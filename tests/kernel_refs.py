@@ -73,7 +73,7 @@ def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_residual=
     return ((v * torch.rsqrt(var + eps)) * weight.float()).to(out_dtype)
 
 
-def silu_mul(gate_up, out_dtype=None, out=None, block=None):
+def silu_mul(gate_up, out_dtype=None, out=None, block=None, activation="silu"):
     out_dtype = out_dtype or gate_up.dtype
     gate_up = _sum(gate_up)
     i = gate_up.shape[1] // 2
@@ -82,15 +82,29 @@ def silu_mul(gate_up, out_dtype=None, out=None, block=None):
         g, u = runs[:, :, 0].reshape(-1, i).float(), runs[:, :, 1].reshape(-1, i).float()
     else:
         g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
+    if activation == "gelu_tanh":
+        return (0.5 * g * (1 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3))) * u).to(out_dtype)
+    assert activation == "silu"
     return ((g / (1 + torch.exp(-g))) * u).to(out_dtype)
 
 
+def _pages(kv_layer, nkv, page_size, d, dv):
+    """Views of a cache layer's keys [pages, nkv, page, d] and values [pages, nkv, page, dv] (both layouts)."""
+    if kv_layer.dim() == 5:
+        return kv_layer[:, 0], kv_layer[:, 1]
+    cut = nkv * page_size * d
+    return kv_layer[:, :cut].view(-1, nkv, page_size, d), kv_layer[:, cut:].view(-1, nkv, page_size, dv)
+
+
 def qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, positions, token_req, block_table, kv_layer, nq, nkv, d,
-                       rotary_dim, page_size, write_kv=True, q_out=None):
+                       rotary_dim, page_size, write_kv=True, q_out=None, dv=None):
     qkv = _sum(qkv)
     n = qkv.shape[0]
-    x = qkv.float().view(n, nq + 2 * nkv, d)
-    q, k, v = x[:, :nq], x[:, nq:nq + nkv], x[:, nq + nkv:]
+    dv = dv or d
+    x = qkv.float()
+    q = x[:, :nq * d].view(n, nq, d)
+    k = x[:, nq * d:(nq + nkv) * d].view(n, nkv, d)
+    v = x[:, (nq + nkv) * d:].view(n, nkv, dv)
 
     def norm(t, gain):
         if gain is None:
@@ -112,8 +126,9 @@ def qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, positions, token_req,
         pos = positions.long()
         page = block_table[token_req.long(), pos // page_size].long()
         within = pos % page_size
-        kv_layer[page, 0, :, within] = k.to(kv_layer.dtype)
-        kv_layer[page, 1, :, within] = v.to(kv_layer.dtype)
+        keys, values = _pages(kv_layer, nkv, page_size, d, dv)
+        keys[page, :, within] = k.to(kv_layer.dtype)
+        values[page, :, within] = v.to(kv_layer.dtype)
     return q.reshape(n, nq * d).to(kv_layer.dtype)
 
 
@@ -178,7 +193,7 @@ def uses_tensor_cores(dtype, d):
     return dtype == torch.bfloat16 and d in (64, 128, 192, 256)
 
 
-def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0):
+def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0, softcap=None, dv=None):
     return 32
 
 
@@ -201,30 +216,34 @@ class DecodePlan:
     stages: int = 0
 
 
-def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len, even=False):
+def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len, even=False, dv=None):
     if requests == 0:
         return DecodePlan(1, False, 0, "single")
     splits = 2 if max_seq_len >= 32 else 1
-    return DecodePlan(splits, FUSE_DECODE, decode_scratch_floats(requests, nq, d, splits), "wave" if splits > 1 else "single")
+    fused = FUSE_DECODE and (dv or d) == d
+    return DecodePlan(splits, fused, decode_scratch_floats(requests, nq, dv or d, splits), "wave" if splits > 1 else "single")
 
 
 def decode_scratch_floats(requests, nq, d, splits):
     return requests * nq * splits * (d + 2) if splits > 1 else 0
 
 
-def _gather_kv(kv_layer, table_row, length, page_size):
+def _gather_kv(kv_layer, table_row, length, page_size, nkv=None, d=None, dv=None):
     pos = torch.arange(length, device=kv_layer.device)
     page = table_row[(pos // page_size)].long()
-    k = kv_layer[page, 0, :, pos % page_size]          # [length, nkv, d]
-    v = kv_layer[page, 1, :, pos % page_size]
+    keys, values = _pages(kv_layer, nkv, page_size, d, dv)
+    k = keys[page, :, pos % page_size]                 # [length, nkv, d]
+    v = values[page, :, pos % page_size]
     return k.float(), v.float()
 
 
-def _attend(q, k, v, q_pos, scale, window):
-    """q [rows, nq, d] at positions q_pos [rows]; k, v [keys, nkv, d] at positions 0..keys-1."""
+def _attend(q, k, v, q_pos, scale, window, softcap=None):
+    """q [rows, nq, d] at positions q_pos [rows]; k [keys, nkv, d], v [keys, nkv, dv] at positions 0..keys-1."""
     rep = q.shape[1] // k.shape[1]
     kk, vv = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
     s = torch.einsum("qhd,khd->hqk", q, kk) * scale
+    if softcap:
+        s = softcap * torch.tanh(s / softcap)
     kpos = torch.arange(k.shape[0], device=q.device)
     seen = kpos[None, :] <= q_pos[:, None]
     if window:
@@ -234,27 +253,29 @@ def _attend(q, k, v, q_pos, scale, window):
 
 
 def attention_prefill(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out, nq, nkv, d,
-                      page_size, scale, window=None, tile_rows=None, heads_per_block=0):
+                      page_size, scale, window=None, tile_rows=None, heads_per_block=0, softcap=None, dv=None):
+    dv = dv or d
     for r in sorted(set(tile_req.tolist())):
         t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
         prefix = int(prefix_lens[r])
-        k, v = _gather_kv(kv_layer, block_table[r], prefix + t1 - t0, page_size)
+        k, v = _gather_kv(kv_layer, block_table[r], prefix + t1 - t0, page_size, nkv, d, dv)
         qpos = torch.arange(prefix, prefix + t1 - t0, device=q.device)
-        o = _attend(q[t0:t1].float().view(-1, nq, d), k, v, qpos, scale, window)
-        out[t0:t1] = o.reshape(t1 - t0, nq * d).to(out.dtype)
+        o = _attend(q[t0:t1].float().view(-1, nq, d), k, v, qpos, scale, window, softcap)
+        out[t0:t1] = o.reshape(t1 - t0, nq * dv).to(out.dtype)
 
 
 def attention_decode(q, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv, d, page_size, scale,
-                     window=None, stages=0):
+                     window=None, stages=0, softcap=None, dv=None):
+    dv = dv or d
     for r in range(q.shape[0]):
         n = int(seq_lens[r])
-        k, v = _gather_kv(kv_layer, block_table[r], n, page_size)
-        o = _attend(q[r:r + 1].float().view(1, nq, d), k, v, torch.tensor([n - 1], device=q.device), scale, window)
-        out[r] = o.reshape(nq * d).to(out.dtype)
+        k, v = _gather_kv(kv_layer, block_table[r], n, page_size, nkv, d, dv)
+        o = _attend(q[r:r + 1].float().view(1, nq, d), k, v, torch.tensor([n - 1], device=q.device), scale, window, softcap)
+        out[r] = o.reshape(nq * dv).to(out.dtype)
 
 
 def attention_decode_fused(qkv, q_gain, k_gain, eps, cos, sin, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv,
-                           d, rotary_dim, page_size, scale, window=None, write_kv=True, stages=0):
+                           d, rotary_dim, page_size, scale, window=None, write_kv=True, stages=0, softcap=None):
     """What the one kernel does, as the two statements it replaces: every request brings one token, at position
     seq_len - 1."""
     qkv = _sum(qkv)
@@ -262,7 +283,78 @@ def attention_decode_fused(qkv, q_gain, k_gain, eps, cos, sin, kv_layer, block_t
     q = qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, (seq_lens - 1).to(torch.int32),
                            torch.arange(n, dtype=torch.int32, device=qkv.device), block_table, kv_layer, nq, nkv, d, rotary_dim,
                            page_size, write_kv=write_kv)
-    attention_decode(q.to(out.dtype), kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv, d, page_size, scale, window)
+    attention_decode(q.to(out.dtype), kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv, d, page_size, scale, window,
+                     softcap=softcap)
+
+
+def sigmoid_gate(out, gate):
+    out.copy_((out.float() * torch.sigmoid(_sum(gate).float())).to(out.dtype))
+    return out
+
+
+def normed_mean(inputs, gains, eps, add=None):
+    total = 0
+    for t, g in zip(inputs, gains):
+        v = _sum(t).float()
+        total = total + (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)) * g.float()
+    total = total / len(inputs)
+    if add is not None:
+        total = total + _sum(add).float()
+    return total.unsqueeze(0)
+
+
+SSM_CHUNK = 64
+
+
+def token_chunks(new_lens, chunk, device):
+    pairs = [(r, s) for r, n in enumerate(new_lens) for s in range(0, n, chunk)]
+    both = torch.tensor([[r for r, _ in pairs], [s for _, s in pairs]], dtype=torch.int32).reshape(2, -1).to(device)
+    return both[0].contiguous(), both[1].contiguous()
+
+
+def causal_conv_silu(proj, col0, channels, weight, bias, state, state_off, chunk_req, chunk_start, cu_seqlens, slots,
+                     chunk=SSM_CHUNK):
+    taps = weight.shape[1]
+    out = torch.empty((proj.shape[0], channels), dtype=proj.dtype, device=proj.device)
+    for r in range(cu_seqlens.numel() - 1):
+        t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+        if t1 == t0:
+            continue
+        held = state[int(slots[r]), state_off:state_off + (taps - 1) * channels].view(taps - 1, channels)
+        seq = torch.cat([held, proj[t0:t1, col0:col0 + channels].float()])
+        acc = (bias.float() if bias is not None else torch.zeros(channels))[None, :].expand(t1 - t0, channels).clone()
+        for j in range(taps):
+            acc = acc + seq[j:j + t1 - t0] * weight[:, j][None, :]
+        out[t0:t1] = (acc * torch.sigmoid(acc)).to(proj.dtype)
+        if taps > 1:
+            held.copy_(seq[-(taps - 1):])
+    return out
+
+
+def ssd_scan(xbc, proj, dt_col, dt_bias, a_log, d_skip, state, cu_seqlens, slots, requests, heads, head_dim, n_state, groups):
+    inner = heads * head_dim
+    y = torch.empty((xbc.shape[0], inner), dtype=torch.float32, device=xbc.device)
+    per = heads // groups
+    a = -torch.exp(a_log.float())
+    for r in range(requests):
+        t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+        s = state[int(slots[r]), :inner * n_state].view(heads, head_dim, n_state)
+        for t in range(t0, t1):
+            x = xbc[t, :inner].float().view(heads, head_dim)
+            b = xbc[t, inner:inner + groups * n_state].float().view(groups, n_state).repeat_interleave(per, 0)
+            c = xbc[t, inner + groups * n_state:].float().view(groups, n_state).repeat_interleave(per, 0)
+            dt = torch.nn.functional.softplus(proj[t, dt_col:dt_col + heads].float() + dt_bias.float())
+            s.copy_(torch.exp(a * dt)[:, None, None] * s + (dt[:, None] * x)[:, :, None] * b[:, None, :])
+            y[t] = (torch.einsum("hpn,hn->hp", s, c) + d_skip.float()[:, None] * x).reshape(inner)
+    return y
+
+
+def gated_group_rmsnorm(y, proj, gain, groups, eps):
+    n, inner = y.shape
+    z = proj[:, :inner].float()
+    v = (y * (z * torch.sigmoid(z))).view(n, groups, inner // groups)
+    v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    return (v.view(n, inner) * gain.float()).to(proj.dtype)
 
 
 def argmax(logits, out=None):
