@@ -50,8 +50,10 @@ def runner_for(path, device, dtype="float32", max_tokens=512, page_size=16, max_
                        max_requests=max_requests, context_length=1024)
 
 
-def dtypes(device):
-    return ["float32"] if device == "cpu" else ["float32", "bfloat16"]
+def dtypes(device, cfg=None):
+    """bfloat16 on the GPU too, except for the configuration whose near one-hot attention turns a rounding of a score
+    into another key (it is there for the exact comparison in float32)."""
+    return ["float32"] if device == "cpu" or cfg is zm.SHARP else ["float32", "bfloat16"]
 
 
 @pytest.mark.parametrize("device", DEVICES)
@@ -60,7 +62,7 @@ def test_whole_decoded_and_in_portions(setup, device):
     page borders); portions of changing sizes down to two tokens and single tokens between them."""
     cfg, weights, path = setup
     ids = zm.tokens(150, cfg["vocab"], 5)
-    for dtype in dtypes(device):
+    for dtype in dtypes(device, cfg):
         want = plain_logits(cfg, weights, ids, dtype)
         runner = runner_for(path, device, dtype)
         close(run_whole(runner, ids), want, dtype, "whole")
@@ -80,7 +82,7 @@ def test_mixed_batches_with_pages_and_slots_used_again(setup, device):
     plan = [{"a": 30, "b": 2, "c": 17}, {"a": 1, "b": 20, "c": 2, "d": 33}, {"a": 1, "b": 1, "c": 1},
             {"a": 28, "b": 18, "c": 50}, {"a": 1, "e": 16}, {"a": 1, "e": 1, "f": 3}, {"a": 28, "e": 41, "f": 17}]
     ends = {1: ["d"], 3: ["b", "c"]}
-    for dtype in dtypes(device):
+    for dtype in dtypes(device, cfg):
         runner = runner_for(path, device, dtype, max_tokens=16 * 16)
         got = run_mixed(runner, reqs, plan, ends)
         for k, ids in reqs.items():
@@ -111,7 +113,7 @@ def test_long_decoding_through_graphs(setup, device):
     cfg, weights, path = setup
     reqs = {k: zm.tokens(n, cfg["vocab"], 90 + i) for i, (k, n) in enumerate({"a": 100, "b": 81, "c": 75}.items())}
     plan = [{"a": 30, "b": 11, "c": 5}] + [{"a": 1, "b": 1, "c": 1}] * 70
-    for dtype in dtypes(device):
+    for dtype in dtypes(device, cfg):
         runner = runner_for(path, device, dtype)
         before = runner.graph_steps
         got = run_mixed(runner, reqs, plan)
