@@ -148,18 +148,19 @@ class Attention(Mixer):
         shared by every layer with the same sizes (``batch.plan``)."""
         s, ops = self.spec, self.ctx.ops
         key = ("attention", group, s.num_heads, s.num_kv_heads, s.head_dim, dtype, page, s.value_dim, bool(s.softcap))
-        dv = s.value_dim
+        sized = {} if s.value_dim == s.head_dim else {"dv": s.value_dim}      # options go to the kernels' faces only
+        capped = {"softcap": s.softcap} if s.softcap else {}                  # where the spec sets them
 
         def make(b):
             nd = b.num_decode
             decode = ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
-                                               even=b.decode_even, dv=dv)
+                                               even=b.decode_even, **sized)
             if decode != ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
-                                                   even=not b.decode_even, dv=dv):
+                                                   even=not b.decode_even, **sized):
                 b.even_asked = True              # a captured step with this plan serves batches of this kind only
             rows = tiles = None
             if b.num_requests > nd:
-                rows = ops.prefill_tile_rows(dtype, s.head_dim, page, b.num_tokens - nd, softcap=s.softcap, dv=dv)
+                rows = ops.prefill_tile_rows(dtype, s.head_dim, page, b.num_tokens - nd, **capped, **sized)
                 tiles = ops.prefill_tiles(b.h_prefix_lens, b.h_new_lens, nd, rows, b.token_ids.device)
             return AttentionPlan(decode, rows, tiles)
         return batch.plan(key, make)
@@ -168,6 +169,8 @@ class Attention(Mixer):
         s, ops = self.spec, self.ctx.ops
         page = self.ctx.page_size
         dv = s.value_dim
+        sized = {} if dv == s.head_dim else {"dv": dv}
+        capped = {"softcap": s.softcap} if s.softcap else {}
         table = batch.block_tables[cache.group]
         plan = self._plan(batch, cache.group, cache.data.dtype, page)
         qkv = ops.linear_auto(x, self.w_qkv, self.b_qkv)
@@ -181,23 +184,23 @@ class Attention(Mixer):
             out = torch.empty((nd, s.num_heads * s.head_dim), dtype=cache.data.dtype, device=cache.data.device)
             ops.attention_decode_fused(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, cache.data, table, batch.seq_lens,
                                        out, scratch, dec.splits, s.num_heads, s.num_kv_heads, s.head_dim, rotary_dim, page,
-                                       self.scale, s.window, write_kv=write_cache, stages=dec.stages, softcap=s.softcap)
+                                       self.scale, s.window, write_kv=write_cache, stages=dec.stages, **capped)
             if gate is not None:
                 ops.sigmoid_gate(out, gate)
             return ops.linear_auto(out, self.w_o, self.b_o)
         q = ops.qk_norm_rope_write(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, batch.positions,
                                    batch.token_req, table, cache.data, s.num_heads, s.num_kv_heads, s.head_dim,
-                                   rotary_dim, page, write_kv=write_cache, dv=dv)
+                                   rotary_dim, page, write_kv=write_cache, **sized)
         out = torch.empty((q.shape[0], s.num_heads * dv), dtype=q.dtype, device=q.device)
         if nd:
             ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, dec.splits,
                                  s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window, stages=dec.stages,
-                                 softcap=s.softcap, dv=dv)
+                                 **capped, **sized)
         if batch.num_requests > nd:
             tile_req, tile_start = plan.tiles
             ops.attention_prefill(q, cache.data, table, batch.cu_seqlens, batch.prefix_lens, tile_req, tile_start,
                                   out, s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window,
-                                  tile_rows=plan.tile_rows, softcap=s.softcap, dv=dv)
+                                  tile_rows=plan.tile_rows, **capped, **sized)
         if gate is not None:
             ops.sigmoid_gate(out, gate)
         return ops.linear_auto(out, self.w_o, self.b_o)
