@@ -45,7 +45,7 @@ constexpr uint32_t SPIN_LIMIT = 1u << 24;     // ~ a second of polling before a 
 
 __device__ int g_status = 0;                  // 0 ok; else (code << 16 | block) of the first wait that gave up
 
-enum Epilogue : int { kPlain = 0, kSiluMul = 1 };
+enum Epilogue : int { kPlain = 0, kSiluMul = 1, kGeluMul = 2 };     // 2: the tanh form of GELU in place of SiLU
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -155,7 +155,9 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tbase, __nv_bfloat16* __r
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
                     const float gv = __uint_as_float(gte[e]);
-                    f[e] = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(up[e]);
+                    // act(g) = g * sigmoid(t): t = g for SiLU, 2 sqrt(2/pi) (g + 0.044715 g^3) for the tanh form of GELU
+                    const float t = EPI == kGeluMul ? 1.5957691216057308f * (gv + 0.044715f * gv * gv * gv) : gv;
+                    f[e] = __fdividef(gv, 1.f + __expf(-t)) * __uint_as_float(up[e]);
                 }
                 if (col + 32 <= N / 2 && (ldc & 7) == 0) {
 #pragma unroll
@@ -575,9 +577,10 @@ LILY_API int lily_gemm_tc(const void* A, const void* B, void* C, const void* bia
     LILY_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0 && lda >= K, "gemm_tc: K=%d, lda=%d must be multiples of 8", K, lda);
     LILY_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0) && ((uintptr_t)C % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
     int rc;
-    if (epilogue == tc::kSiluMul) {
-        LILY_REQUIRE(N % 256 == 0 && bias == nullptr && ldc >= N / 2, "gemm_tc: the SiLU*mul epilogue takes N %% 256 == 0 and no bias");
-        rc = tc::launch<tc::kSiluMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream);
+    if (epilogue == tc::kSiluMul || epilogue == tc::kGeluMul) {
+        LILY_REQUIRE(N % 256 == 0 && bias == nullptr && ldc >= N / 2, "gemm_tc: the gate*up epilogue takes N %% 256 == 0 and no bias");
+        rc = epilogue == tc::kSiluMul ? tc::launch<tc::kSiluMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream)
+                                      : tc::launch<tc::kGeluMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream);
     } else {
         LILY_REQUIRE(epilogue == tc::kPlain && ldc >= N, "gemm_tc: epilogue %d, ldc %d", epilogue, ldc);
         rc = tc::launch<tc::kPlain>(A, B, C, bias, M, N, K, lda, ldc, stream);

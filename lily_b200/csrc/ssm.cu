@@ -77,11 +77,12 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
 
 // ---------------------------------------------------------------------------- selective scan
 
-// grid (heads, requests, ceil(head_dim / pb)), block pb * ns threads: `ns` neighbouring lanes share one value
-// column p of the head's state and hold every ns-th of its `n_state` entries in registers (NPT each); the
-// tokens of the request run one after another, staged `tt` at a time in shared memory (B and C of the head's
-// group, the head's x, step sizes and decays).
-template <typename T, int NPT>
+// grid (heads, requests, ceil(head_dim / pb)), block (pb / PC) * ns threads: `ns` neighbouring lanes share PC
+// neighbouring value columns of the head's state and hold every ns-th of their `n_state` entries in registers (NPT
+// a column: PC * NPT numbers a thread, so that one B and one C entry read from shared memory serve 2 * PC
+// multiply-adds); the tokens of the request run one after another, staged `tt` at a time in shared memory (B and C
+// of the head's group, the head's x, step sizes and decays).
+template <typename T, int NPT, int PC>
 __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ proj, int proj_stride,
                                 int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ d_skip, float* __restrict__ state, size_t state_stride,
@@ -91,8 +92,7 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
     extern __shared__ float smem[];
     pdl_enter_small();
     const int h = blockIdx.x, r = blockIdx.y, p0 = blockIdx.z * pb;
-    const int tid = threadIdx.x, j = tid % ns, pl = tid / ns, p = p0 + pl;
-    const bool active = p < pd;
+    const int tid = threadIdx.x, j = tid % ns, pl = (tid / ns) * PC, p = p0 + pl;     // this thread's first column
     const int tok0 = cu_seqlens[r], len = cu_seqlens[r + 1] - tok0;
     if (len <= 0) return;
     float* Bs = smem;                        // [tt][n_state]
@@ -103,12 +103,15 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
     const int inner = heads * pd;
     const int g = h / (heads / groups);
     const int bcol = inner + g * n_state, ccol = inner + (groups + g) * n_state;
-    float* st = state + (size_t)slots[r] * state_stride + ((size_t)h * pd + (active ? p : 0)) * n_state;
-    float S[NPT];
+    float* st = state + (size_t)slots[r] * state_stride + (size_t)h * pd * n_state;
+    float S[PC][NPT];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-        const int n = i * ns + j;
-        S[i] = (active && n < n_state) ? st[n] : 0.f;
+    for (int c = 0; c < PC; ++c) {
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int n = i * ns + j;
+            S[c][i] = (p + c < pd && n < n_state) ? st[(size_t)(p + c) * n_state + n] : 0.f;
+        }
     }
     const float A = -expf(a_log[h]), bias = dt_bias[h], D = d_skip[h];
     for (int t0 = 0; t0 < len; t0 += tt) {
@@ -131,27 +134,41 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
         }
         __syncthreads();
         for (int ti = 0; ti < now; ++ti) {
-            const float xv = xs[ti * pb + pl], da = das[ti], coef = dts[ti] * xv;
+            const float da = das[ti], dtv = dts[ti];
             const float* bt = Bs + ti * n_state;
             const float* ct = Cs + ti * n_state;
-            float acc = 0.f;
+            float xv[PC], coef[PC], acc[PC];
+#pragma unroll
+            for (int c = 0; c < PC; ++c) {
+                xv[c] = xs[ti * pb + pl + c];
+                coef[c] = dtv * xv[c];
+                acc[c] = 0.f;
+            }
 #pragma unroll
             for (int i = 0; i < NPT; ++i) {
                 const int n = i * ns + j;
                 if (n < n_state) {
-                    S[i] = fmaf(da, S[i], coef * bt[n]);
-                    acc = fmaf(S[i], ct[n], acc);
+                    const float bn = bt[n], cn = ct[n];
+#pragma unroll
+                    for (int c = 0; c < PC; ++c) {
+                        S[c][i] = fmaf(da, S[c][i], coef[c] * bn);
+                        acc[c] = fmaf(S[c][i], cn, acc[c]);
+                    }
                 }
             }
-            for (int o = ns >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (j == 0 && active) y[(size_t)(tok0 + t0 + ti) * inner + h * pd + p] = fmaf(D, xv, acc);
+#pragma unroll
+            for (int c = 0; c < PC; ++c) {
+                for (int o = ns >> 1; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+                if (j == 0 && p + c < pd) y[(size_t)(tok0 + t0 + ti) * inner + h * pd + p + c] = fmaf(D, xv[c], acc[c]);
+            }
         }
     }
-    if (active) {
+#pragma unroll
+    for (int c = 0; c < PC; ++c) {
 #pragma unroll
         for (int i = 0; i < NPT; ++i) {
             const int n = i * ns + j;
-            if (n < n_state) st[n] = S[i];
+            if (p + c < pd && n < n_state) st[(size_t)(p + c) * n_state + n] = S[c][i];
         }
     }
 }
@@ -221,28 +238,35 @@ LILY_API int lily_ssd_scan(const void* xbc, int channels, const void* proj, int 
     LILY_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0, "ssd_scan: %d heads over %d groups", heads, groups);
     LILY_REQUIRE(n_state >= 1 && n_state <= 512 && pd >= 1, "ssd_scan: state %d (1 to 512), head size %d", n_state, pd);
     LILY_REQUIRE(requests <= 65535, "ssd_scan: %d requests", requests);
-    // ns lanes share a value column, each with npt = 4, 8 or 16 entries of its state
+    // ns lanes share pc value columns, each lane with npt = 4, 8 or 16 entries of a column's state
     int npt = n_state <= 32 ? 4 : (n_state <= 128 ? 8 : 16);
     int ns = 1;
     while (ns * npt < n_state) ns <<= 1;
     if (ns > 32) { ns = 32; npt = 16; }
-    int pb = 256 / ns;                                   // value columns a block
-    while (pb > 32 / ns && pb / 2 >= pd) pb >>= 1;       // no wider than the head, but whole warps
-    if (pb < 32 / ns) pb = 32 / ns;
-    if (pb < 1) pb = 1;
+    if (npt == 8 && ns >= 16) { npt = 16; ns >>= 1; }    // fewer lanes to add up over
+    int pc = pd % 4 == 0 && pd >= 16 ? 4 : (pd % 2 == 0 && pd >= 8 ? 2 : 1);
+    const int lanes_cols = 32 / ns > 0 ? 32 / ns : 1;    // column groups that fill a warp
+    int groups_needed = (pd + pc - 1) / pc;              // column groups of a head
+    int cg = groups_needed;                              // column groups a block: the whole head when it fits 256 threads
+    while (cg * ns > 256) cg = (cg + 1) / 2;
+    cg = (cg + lanes_cols - 1) / lanes_cols * lanes_cols;    // whole warps
+    const int pb = cg * pc;
     int tt = 16;
     while (tt > 1 && (size_t)tt * (2 * n_state + pb + 2) * sizeof(float) > 40 * 1024) tt >>= 1;
+    // (a block is whole warps, so it has at least as many threads as a stage has tokens)
     const size_t smem = (size_t)tt * (2 * n_state + pb + 2) * sizeof(float);
-    dim3 grid(heads, requests, (pd + pb - 1) / pb), block(pb * ns);
-#define GO(T, N)                                                                                                       \
-    launch_pdl(ssd_scan_kernel<T, N>, grid, block, smem, stream, (const T*)xbc, channels, (const T*)proj, proj_stride,  \
+    dim3 grid(heads, requests, (pd + pb - 1) / pb), block(cg * ns);
+#define GO(T, N, C)                                                                                                    \
+    launch_pdl(ssd_scan_kernel<T, N, C>, grid, block, smem, stream, (const T*)xbc, channels, (const T*)proj, proj_stride, \
                dt_col, dt_bias, a_log, d_skip, state, state_stride, y, cu_seqlens, slots, heads, pd, n_state, groups, ns, \
                pb, tt)
+#define GO_C(T, N) do { if (pc == 4) GO(T, N, 4); else if (pc == 2) GO(T, N, 2); else GO(T, N, 1); } while (0)
     if (dtype == kBF16) {
-        if (npt == 4) GO(__nv_bfloat16, 4); else if (npt == 8) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 16);
+        if (npt == 4) GO_C(__nv_bfloat16, 4); else if (npt == 8) GO_C(__nv_bfloat16, 8); else GO_C(__nv_bfloat16, 16);
     } else {
-        if (npt == 4) GO(float, 4); else if (npt == 8) GO(float, 8); else GO(float, 16);
+        if (npt == 4) GO_C(float, 4); else if (npt == 8) GO_C(float, 8); else GO_C(float, 16);
     }
+#undef GO_C
 #undef GO
     LILY_CHECK_LAUNCH("ssd_scan");
     return 0;

@@ -1,5 +1,5 @@
 """Dense gated feed-forward: ``down(act(gate(x)) * up(x))``, no bias; act is SiLU (SwiGLU) unless the spec names
-another (``"gelu_tanh"``: the product and the activation kernel then run separately).
+another (``"gelu_tanh"``); the fused kernels take either.
 
 gate and up are one matrix ``[2 * inter, hidden]`` so that one product feeds the SiLU*mul
 (lily/models/llama.py:31-47, stacking llama.py:164-165).  In bfloat16, when the intermediate size
@@ -69,16 +69,14 @@ class SwiGLU(FeedForward):
     def forward(self, x, batch):
         ops = self.ctx.ops
         product = ops.linear_auto                                # partial sums for a few tokens, else [M, N]
-        if self.spec.activation != "silu":
-            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, block=self.block, activation=self.spec.activation)
-            return product(act, self.w_down)
+        how = {} if self.spec.activation == "silu" else {"activation": self.spec.activation}
         few = ops.swiglu_skinny_need(x.shape[0], self.spec.intermediate_size, self.spec.hidden_size, x.dtype, self.block)
         if few is not None and batch.workspace is not None:
-            # a few tokens: one kernel streams the fused matrix and applies SiLU*mul to its own sums
+            # a few tokens: one kernel streams the fused matrix and applies the activation and the product to its own sums
             act = ops.swiglu_skinny(x, self.w_gate_up, self.block, batch.workspace.floats("swiglu", few[0]),
-                                    batch.workspace.counters("swiglu", few[1]))
+                                    batch.workspace.counters("swiglu", few[1]), **how)
         elif self.block and ops.gate_up_fused_pays(x.shape[0], self.w_gate_up.shape[0]) and ops.gemm_tc_takes(x, self.w_gate_up):
-            act = ops.gemm_tc(x, self.w_gate_up, silu_mul_block=True)
+            act = ops.gemm_tc(x, self.w_gate_up, silu_mul_block=True, **how)
         else:
-            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, block=self.block)
+            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, block=self.block, **how)
         return product(act, self.w_down)
