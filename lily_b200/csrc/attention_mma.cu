@@ -417,8 +417,11 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         }
     }
     // scores are kept in units of log2(e); with a soft cap they are capped first and then carry no further scale
+    // (the hardware's tanh, relative error about 2^-11: the weights are rounded to bfloat16 for the p . v product anyway;
+    // the float32 path is the CUDA-core kernel's, which calls tanhf)
     const float cap = a.softcap, cap_in = cap > 0.f ? a.scale / cap : 0.f;
     const float sl2 = (cap > 0.f ? 1.f : a.scale) * 1.4426950408889634f;
+    auto tanh_fast = [](float v) { float r; asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v)); return r; };
 
     for (int t = 0; t < ntiles; ++t) {
         const int buf = t % STAGES;
@@ -452,7 +455,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) s[j][e] = cap * tanhf(s[j][e] * cap_in);
+                for (int e = 0; e < 4; ++e) s[j][e] = cap * tanh_fast(s[j][e] * cap_in);
             }
         }
 

@@ -22,6 +22,23 @@ struct Operand {
         for (int s = 1; s < splits; ++s) v += f[i + (size_t)s * stride];
         return v;
     }
+    // four consecutive entries from a multiple of four (16-byte aligned base, stride a multiple of four)
+    __device__ __forceinline__ float4 four(size_t i) const {
+        if (bf16) {
+            const uint2 raw = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)p + i);
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            return make_float4(lo.x, lo.y, hi.x, hi.y);
+        }
+        const float* f = (const float*)p;
+        float4 v = *reinterpret_cast<const float4*>(f + i);
+        for (int s = 1; s < splits; ++s) {
+            const float4 t = *reinterpret_cast<const float4*>(f + i + (size_t)s * stride);
+            v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+        }
+        return v;
+    }
+    bool vector_ok() const { return p == nullptr || (((uintptr_t)p & 15) == 0 && stride % 4 == 0); }
 };
 
 constexpr int MEAN_MAX = 4;
@@ -44,7 +61,26 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ out, const Operand gate, siz
         out[i] = from_float<T>(to_float(out[i]) / (1.f + expf(-gate(i))));
 }
 
-// One block a token.
+// bfloat16 in place with a bfloat16 gate in one piece, eight entries a thread and turn (16-byte accesses)
+__global__ void sigmoid_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate, size_t total) {
+    pdl_enter_small();
+    const size_t step = (size_t)gridDim.x * blockDim.x * 8;
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < total; i += step) {
+        uint4 ov = *reinterpret_cast<const uint4*>(out + i);
+        const uint4 gv = *reinterpret_cast<const uint4*>(gate + i);
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 o = __bfloat1622float2(o2[k]), g = __bfloat1622float2(g2[k]);
+            o2[k] = __floats2bfloat162_rn(__fdividef(o.x, 1.f + __expf(-g.x)), __fdividef(o.y, 1.f + __expf(-g.y)));
+        }
+        *reinterpret_cast<uint4*>(out + i) = ov;
+    }
+}
+
+// One block a token.  VEC 4: four columns a thread and turn (the width a multiple of four, everything 16-byte aligned).
+template <int VEC>
 __global__ void normed_mean_kernel(const NormedMeanArgs a) {
     __shared__ float red[33];
     pdl_enter_small();
@@ -55,21 +91,45 @@ __global__ void normed_mean_kernel(const NormedMeanArgs a) {
         inv[k] = 0.f;
         if (k < a.count) {
             float ssq = 0.f;
-            for (int i = threadIdx.x; i < a.width; i += blockDim.x) {
-                const float v = a.in[k](base + i);
-                ssq = fmaf(v, v, ssq);
+            for (int i = threadIdx.x * VEC; i < a.width; i += blockDim.x * VEC) {
+                if (VEC == 4) {
+                    const float4 v = a.in[k].four(base + i);
+                    ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                } else {
+                    const float v = a.in[k](base + i);
+                    ssq = fmaf(v, v, ssq);
+                }
             }
             inv[k] = rsqrtf(block_sum(ssq, red) / (float)a.width + a.eps);
         }
     }
-    for (int i = threadIdx.x; i < a.width; i += blockDim.x) {
-        float o = 0.f;
+    for (int i = threadIdx.x * VEC; i < a.width; i += blockDim.x * VEC) {
+        if (VEC == 4) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int k = 0; k < MEAN_MAX; ++k)
-            if (k < a.count) o += (a.in[k](base + i) * inv[k]) * a.gain[k][i];
-        o *= a.scale;
-        if (a.add.p) o += a.add(base + i);
-        a.out[base + i] = o;
+            for (int k = 0; k < MEAN_MAX; ++k) {
+                if (k < a.count) {
+                    const float4 v = a.in[k].four(base + i);
+                    const float4 g = *reinterpret_cast<const float4*>(a.gain[k] + i);
+                    o.x += (v.x * inv[k]) * g.x; o.y += (v.y * inv[k]) * g.y;
+                    o.z += (v.z * inv[k]) * g.z; o.w += (v.w * inv[k]) * g.w;
+                }
+            }
+            o.x *= a.scale; o.y *= a.scale; o.z *= a.scale; o.w *= a.scale;
+            if (a.add.p) {
+                const float4 f = a.add.four(base + i);
+                o.x += f.x; o.y += f.y; o.z += f.z; o.w += f.w;
+            }
+            *reinterpret_cast<float4*>(a.out + base + i) = o;
+        } else {
+            float o = 0.f;
+#pragma unroll
+            for (int k = 0; k < MEAN_MAX; ++k)
+                if (k < a.count) o += (a.in[k](base + i) * inv[k]) * a.gain[k][i];
+            o *= a.scale;
+            if (a.add.p) o += a.add(base + i);
+            a.out[base + i] = o;
+        }
     }
 }
 
@@ -83,7 +143,11 @@ LILY_API int lily_sigmoid_gate(void* out, int out_dtype, const void* gate, int g
     LILY_REQUIRE(gate_splits >= 1 && (gate_splits == 1 || gate_dtype == kF32), "sigmoid_gate: only float32 partial sums come in several splits");
     const Operand g{gate, gate_dtype == kBF16, gate_splits, gate_stride};
     const int blocks = (int)((total + 255) / 256 < (size_t)sm_count() * 16 ? (total + 255) / 256 : (size_t)sm_count() * 16);
-    if (out_dtype == kBF16) launch_pdl(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, g, total);
+    if (out_dtype == kBF16 && gate_dtype == kBF16 && total % 8 == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)gate & 15) == 0) {
+        const size_t work = total / 8;
+        const int b8 = (int)((work + 255) / 256 < (size_t)sm_count() * 16 ? (work + 255) / 256 : (size_t)sm_count() * 16);
+        launch_pdl(sigmoid_gate_bf16x8_kernel, dim3(b8), dim3(256), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, total);
+    } else if (out_dtype == kBF16) launch_pdl(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, g, total);
     else launch_pdl(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, g, total);
     LILY_CHECK_LAUNCH("sigmoid_gate");
     return 0;
@@ -107,7 +171,13 @@ LILY_API int lily_normed_mean(const void* const* ins, const int* dtypes, const i
     a.count = count;
     a.add = Operand{add, add_dtype == kBF16, add_splits < 1 ? 1 : add_splits, add_stride};
     a.out = out; a.width = width; a.eps = eps; a.scale = scale;
-    launch_pdl(normed_mean_kernel, dim3(tokens), dim3(width >= 2048 ? 512 : 256), 0, stream, a);
+    bool vec = width % 4 == 0 && a.add.vector_ok() && ((uintptr_t)out & 15) == 0;
+    for (int k = 0; k < count; ++k) vec = vec && a.in[k].vector_ok() && ((uintptr_t)gains[k] & 15) == 0;
+    // a few tokens: the block as wide as the row allows (few blocks are in flight, each should be short)
+    int threads = width >= 2048 ? 512 : 256;
+    if (tokens <= 64 && vec) threads = width / 4 >= 1024 ? 1024 : (width / 4 >= 512 ? 512 : threads);
+    if (vec) launch_pdl(normed_mean_kernel<4>, dim3(tokens), dim3(threads), 0, stream, a);
+    else launch_pdl(normed_mean_kernel<1>, dim3(tokens), dim3(threads), 0, stream, a);
     LILY_CHECK_LAUNCH("normed_mean");
     return 0;
 }

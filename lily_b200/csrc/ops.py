@@ -46,7 +46,9 @@ _SIGNATURES = {
     "lily_sigmoid_gate": [_vp, _i, _vp, _i, _i, _sz, _sz, _vp],
     "lily_normed_mean": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _sz, _vp, _i, _i, _f, _f, _vp],
     "lily_causal_conv_silu": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _vp],
-    "lily_ssd_scan": [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "lily_ssd_scan": [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp,
+                      _i, _vp, _vp, _vp],
+    "lily_ssd_combine": [_vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lily_gated_group_rmsnorm": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -804,15 +806,65 @@ def causal_conv_silu(proj: torch.Tensor, col0: int, channels: int, weight: torch
     return out
 
 
+SCAN_CHUNK = 128        # tokens a chunk of a long portion (doubled while the chunk states would pass SCAN_WORKSPACE)
+SCAN_DIRECT = 192       # portions up to this many tokens run in one piece, from and to the state in the slot
+SCAN_WORKSPACE = 1 << 29
+
+
+@dataclass
+class ScanPlan:
+    """How the selective scan of a step runs: the requests whose new tokens run in one piece (``direct``), and the
+    long portions cut into chunks that run side by side (``scan_plan``).  All lists are int32 on the device."""
+
+    direct: Optional[torch.Tensor]           # request indices, or None when every request runs in one piece
+    num_direct: int
+    chunk_req: Optional[torch.Tensor] = None
+    chunk_start: Optional[torch.Tensor] = None
+    chunk_len: Optional[torch.Tensor] = None
+    num_chunks: int = 0
+    long_req: Optional[torch.Tensor] = None
+    long_first: Optional[torch.Tensor] = None
+    long_count: Optional[torch.Tensor] = None
+    num_long: int = 0
+
+
+def scan_plan(new_lens: Sequence[int], device, state_floats: int = 0) -> ScanPlan:
+    """Cuts the step's portions for the scan.  A portion of up to SCAN_DIRECT tokens (every decoded token) runs in one
+    piece; a longer one in chunks of SCAN_CHUNK tokens that run side by side and are joined by ``ssd_combine``
+    (``state_floats``: the size of one scan state, which bounds how many chunks the workspace may hold)."""
+    longs = [r for r, n in enumerate(new_lens) if n > SCAN_DIRECT]
+    if not longs:
+        return ScanPlan(None, len(new_lens))
+    chunk = SCAN_CHUNK
+    while state_floats and sum(-(-new_lens[r] // chunk) for r in longs) * state_floats * 4 > SCAN_WORKSPACE:
+        chunk *= 2
+    direct = [r for r, n in enumerate(new_lens) if n <= SCAN_DIRECT]
+    creq, cstart, clen, lfirst, lcount = [], [], [], [], []
+    for r in longs:
+        lfirst.append(len(creq))
+        for s in range(0, new_lens[r], chunk):
+            creq.append(r)
+            cstart.append(s)
+            clen.append(min(chunk, new_lens[r] - s))
+        lcount.append(len(creq) - lfirst[-1])
+    flat = direct + creq + cstart + clen + longs + lfirst + lcount
+    dev = torch.tensor(flat, dtype=torch.int32).to(device, non_blocking=True)
+    sizes = [len(direct)] + [len(creq)] * 3 + [len(longs)] * 3
+    parts = torch.split(dev, sizes)
+    return ScanPlan(parts[0], len(direct), parts[1], parts[2], parts[3], len(creq), parts[4], parts[5], parts[6], len(longs))
+
+
 def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
              d_skip: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, requests: int,
-             heads: int, head_dim: int, n_state: int, groups: int) -> torch.Tensor:
+             heads: int, head_dim: int, n_state: int, groups: int, plan: Optional[ScanPlan] = None,
+             workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The selective scan of each request's new tokens from its carried state, per head h of group g:
     ``S = exp(-exp(a_log[h]) dt) S + dt B x^T``, ``y = S^T C + d_skip[h] x`` with ``dt = softplus(proj[:, dt_col + h] +
     dt_bias[h])``, x = ``xbc[:, h * head_dim:]``, B and C = ``xbc[:, heads * head_dim + (g | groups + g) * n_state:]``.
     ``state[slot, :heads * head_dim * n_state]`` holds S as [heads, head_dim, n_state] and is updated in place.
-    Returns y float32 [tokens, heads * head_dim]."""
-    _dev(xbc, proj, dt_bias, a_log, d_skip, state, cu_seqlens, slots)
+    With a ``plan`` (``scan_plan``) long portions run as chunks side by side through ``workspace`` (float32,
+    ``scan_workspace_floats``; made here when absent).  Returns y float32 [tokens, heads * head_dim]."""
+    _dev(xbc, proj, dt_bias, a_log, d_skip, state, cu_seqlens, slots, workspace)
     n, channels = xbc.shape
     inner = heads * head_dim
     if channels != inner + 2 * groups * n_state or proj.dtype != xbc.dtype or proj.shape[0] != n:
@@ -823,10 +875,33 @@ def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.
     if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < inner * n_state or dt_col + heads > proj.shape[1]:
         raise KernelError("ssd_scan: state or dt columns out of range")
     y = torch.empty((n, inner), dtype=torch.float32, device=xbc.device)
-    _call("lily_ssd_scan", _p(xbc), channels, _p(proj), proj.shape[1], int(dt_col), _p(dt_bias), _p(a_log), _p(d_skip),
-          _p(state), state.shape[1], _p(y), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), int(requests), heads,
-          head_dim, n_state, groups, _dt(xbc), _stream())
+    common = (_p(xbc), channels, _p(proj), proj.shape[1], int(dt_col), _p(dt_bias), _p(a_log), _p(d_skip), _p(state),
+              state.shape[1], _p(y), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"))
+    sizes = (heads, head_dim, n_state, groups, _dt(xbc))
+    if plan is None or plan.direct is None:
+        _call("lily_ssd_scan", *common, int(requests), *sizes, None, None, None, 0, None, None, _stream())
+        return y
+    if plan.num_direct:
+        _call("lily_ssd_scan", *common, plan.num_direct, *sizes, _p(plan.direct), None, None, 0, None, None, _stream())
+    need = scan_workspace_floats(plan, heads, head_dim, n_state)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.float32, device=xbc.device)
+    if workspace.dtype != torch.float32 or workspace.numel() < need:
+        raise KernelError(f"ssd_scan: a float32 workspace of {need} entries needed")
+    chunk_state, chunk_decay = workspace, workspace[plan.num_chunks * inner * n_state:]
+    items = (_p(plan.chunk_req), _p(plan.chunk_start), _p(plan.chunk_len))
+    _call("lily_ssd_scan", *common, plan.num_chunks, *sizes, *items, 1, _p(chunk_state), _p(chunk_decay), _stream())
+    _call("lily_ssd_combine", _p(state), state.shape[1], _i32(slots, "slots"), _p(chunk_state), _p(chunk_decay),
+          _p(plan.long_req), _p(plan.long_first), _p(plan.long_count), plan.num_long, heads, head_dim * n_state, _stream())
+    _call("lily_ssd_scan", *common, plan.num_chunks, *sizes, *items, 2, _p(chunk_state), _p(chunk_decay), _stream())
     return y
+
+
+def scan_workspace_floats(plan: Optional[ScanPlan], heads: int, head_dim: int, n_state: int) -> int:
+    """float32 entries ``ssd_scan`` needs for this plan: a state and one decay a head for every chunk."""
+    if plan is None or not plan.num_chunks:
+        return 0
+    return plan.num_chunks * (heads * head_dim * n_state + heads)
 
 
 def gated_group_rmsnorm(y: torch.Tensor, proj: torch.Tensor, gain: torch.Tensor, groups: int, eps: float) -> torch.Tensor:

@@ -58,16 +58,24 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
     for (int j = 0; j < TAPS; ++j) wt[j] = w[(size_t)c * TAPS + j];
     const float b = bias ? bias[c] : 0.f;
     T* dst = out + (size_t)(tok0 + start) * channels + c;
-    for (int t = 0; t < n; ++t) {
-        const float x = to_float(src[(size_t)(start + t) * in_stride]);
-        float acc = b;
+    for (int t = 0; t < n; t += 4) {                 // four tokens' inputs asked for before the first is used
+        float xs[4];
 #pragma unroll
-        for (int j = 0; j < K1; ++j) acc = fmaf(win[j], wt[j], acc);
-        acc = fmaf(x, wt[K1], acc);
+        for (int u = 0; u < 4; ++u) xs[u] = t + u < n ? to_float(src[(size_t)(start + t + u) * in_stride]) : 0.f;
 #pragma unroll
-        for (int j = 0; j + 1 < K1; ++j) win[j] = win[j + 1];
-        if (K1 > 0) win[K1 - 1] = x;
-        dst[(size_t)t * channels] = from_float<T>(silu_f(acc));
+        for (int u = 0; u < 4; ++u) {
+            if (t + u < n) {
+                const float x = xs[u];
+                float acc = b;
+#pragma unroll
+                for (int j = 0; j < K1; ++j) acc = fmaf(win[j], wt[j], acc);
+                acc = fmaf(x, wt[K1], acc);
+#pragma unroll
+                for (int j = 0; j + 1 < K1; ++j) win[j] = win[j + 1];
+                if (K1 > 0) win[K1 - 1] = x;
+                dst[(size_t)(t + u) * channels] = from_float<T>(silu_f(acc));
+            }
+        }
     }
     if (start == 0 && len <= chunk_len) {
 #pragma unroll
@@ -82,18 +90,29 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
 // a column: PC * NPT numbers a thread, so that one B and one C entry read from shared memory serve 2 * PC
 // multiply-adds); the tokens of the request run one after another, staged `tt` at a time in shared memory (B and C
 // of the head's group, the head's x, step sizes and decays).
-template <typename T, int NPT, int PC>
+//
+// A work item (blockIdx.y) is a run of consecutive new tokens of one request.  Without item lists it is a request's
+// whole portion, from the state in the request's slot to the state in the request's slot (mode 0).  A long portion
+// is cut into chunks that run side by side: mode 1 starts each chunk from zero and leaves the chunk's own state and
+// the product of its decays in a workspace (EMIT false: no outputs); a combine kernel then walks the chunks in order,
+// S <- decay_c S + state_c, leaving in the workspace the state each chunk starts from and in the slot the last one;
+// mode 2 runs each chunk again from that state and writes the outputs.
+template <typename T, int NPT, int PC, bool EMIT>
 __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ proj, int proj_stride,
                                 int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ d_skip, float* __restrict__ state, size_t state_stride,
                                 float* __restrict__ y, const int* __restrict__ cu_seqlens,
                                 const int* __restrict__ slots, int heads, int pd, int n_state, int groups, int ns,
-                                int pb, int tt) {
+                                int pb, int tt, const int* __restrict__ item_req, const int* __restrict__ item_start,
+                                const int* __restrict__ item_len, int mode, float* __restrict__ chunk_state,
+                                float* __restrict__ chunk_decay) {
     extern __shared__ float smem[];
     pdl_enter_small();
-    const int h = blockIdx.x, r = blockIdx.y, p0 = blockIdx.z * pb;
+    const int h = blockIdx.x, item = blockIdx.y, p0 = blockIdx.z * pb;
+    const int r = item_req ? item_req[item] : item;
     const int tid = threadIdx.x, j = tid % ns, pl = (tid / ns) * PC, p = p0 + pl;     // this thread's first column
-    const int tok0 = cu_seqlens[r], len = cu_seqlens[r + 1] - tok0;
+    const int tok0 = cu_seqlens[r] + (item_start ? item_start[item] : 0);
+    const int len = item_len ? item_len[item] : cu_seqlens[r + 1] - cu_seqlens[r];
     if (len <= 0) return;
     float* Bs = smem;                        // [tt][n_state]
     float* Cs = Bs + (size_t)tt * n_state;   // [tt][n_state]
@@ -103,17 +122,19 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
     const int inner = heads * pd;
     const int g = h / (heads / groups);
     const int bcol = inner + g * n_state, ccol = inner + (groups + g) * n_state;
-    float* st = state + (size_t)slots[r] * state_stride + (size_t)h * pd * n_state;
+    float* st = (mode == 0 ? state + (size_t)slots[r] * state_stride : chunk_state + (size_t)item * heads * pd * n_state) +
+                (size_t)h * pd * n_state;
     float S[PC][NPT];
 #pragma unroll
     for (int c = 0; c < PC; ++c) {
 #pragma unroll
         for (int i = 0; i < NPT; ++i) {
             const int n = i * ns + j;
-            S[c][i] = (p + c < pd && n < n_state) ? st[(size_t)(p + c) * n_state + n] : 0.f;
+            S[c][i] = (mode != 1 && p + c < pd && n < n_state) ? st[(size_t)(p + c) * n_state + n] : 0.f;
         }
     }
     const float A = -expf(a_log[h]), bias = dt_bias[h], D = d_skip[h];
+    float decayed = 1.f;                     // the product of the item's decays
     for (int t0 = 0; t0 < len; t0 += tt) {
         const int now = min(tt, len - t0);
         __syncthreads();
@@ -135,6 +156,7 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
         __syncthreads();
         for (int ti = 0; ti < now; ++ti) {
             const float da = das[ti], dtv = dts[ti];
+            decayed *= da;
             const float* bt = Bs + ti * n_state;
             const float* ct = Cs + ti * n_state;
             float xv[PC], coef[PC], acc[PC];
@@ -152,17 +174,20 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
 #pragma unroll
                     for (int c = 0; c < PC; ++c) {
                         S[c][i] = fmaf(da, S[c][i], coef[c] * bn);
-                        acc[c] = fmaf(S[c][i], cn, acc[c]);
+                        if (EMIT) acc[c] = fmaf(S[c][i], cn, acc[c]);
                     }
                 }
             }
+            if (EMIT) {
 #pragma unroll
-            for (int c = 0; c < PC; ++c) {
-                for (int o = ns >> 1; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
-                if (j == 0 && p + c < pd) y[(size_t)(tok0 + t0 + ti) * inner + h * pd + p + c] = fmaf(D, xv[c], acc[c]);
+                for (int c = 0; c < PC; ++c) {
+                    for (int o = ns >> 1; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+                    if (j == 0 && p + c < pd) y[(size_t)(tok0 + t0 + ti) * inner + h * pd + p + c] = fmaf(D, xv[c], acc[c]);
+                }
             }
         }
     }
+    if (mode == 2) return;
 #pragma unroll
     for (int c = 0; c < PC; ++c) {
 #pragma unroll
@@ -171,6 +196,29 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
             if (p + c < pd && n < n_state) st[(size_t)(p + c) * n_state + n] = S[c][i];
         }
     }
+    if (mode == 1 && tid == 0 && blockIdx.z == 0) chunk_decay[(size_t)item * heads + h] = decayed;
+}
+
+// grid (ceil(elements / 256), long portions), block 256: one entry of the scan state through the chunks of a portion.
+__global__ void ssd_combine_kernel(float* __restrict__ state, size_t state_stride, const int* __restrict__ slots,
+                                   float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                                   const int* __restrict__ long_req, const int* __restrict__ long_first,
+                                   const int* __restrict__ long_count, int heads, int per_head) {
+    pdl_enter_small();
+    const size_t elements = (size_t)heads * per_head;
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= elements) return;
+    const int k = blockIdx.y, h = (int)(e / per_head);
+    float* st = state + (size_t)slots[long_req[k]] * state_stride + e;
+    float S = *st;
+    const int first = long_first[k], count = long_count[k];
+    for (int c = first; c < first + count; ++c) {
+        float* cs = chunk_state + (size_t)c * elements + e;
+        const float own = *cs;
+        *cs = S;
+        S = fmaf(chunk_decay[(size_t)c * heads + h], S, own);
+    }
+    *st = S;
 }
 
 // ---------------------------------------------------------------------------- gate, then grouped RMSNorm
@@ -188,12 +236,32 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     const float* yr = y + t * inner + c0;
     const T* zr = z + t * z_stride + c0;
     float ssq = 0.f;
-    for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
-        const float v = yr[i] * silu_f(to_float(zr[i]));
-        ssq = fmaf(v, v, ssq);
+    // two columns a thread and turn where the group and the rows allow it (even sizes: 8-byte and 4-byte accesses)
+    const bool pairs = (gsize & 1) == 0 && (inner & 1) == 0 && (z_stride & 1) == 0 && (c0 & 1) == 0;
+    if (pairs) {
+        for (int i = 2 * threadIdx.x; i < gsize; i += 2 * blockDim.x) {
+            const float2 yv = *reinterpret_cast<const float2*>(yr + i);
+            const float v0 = yv.x * silu_f(to_float(zr[i])), v1 = yv.y * silu_f(to_float(zr[i + 1]));
+            ssq += v0 * v0 + v1 * v1;
+        }
+    } else {
+        for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
+            const float v = yr[i] * silu_f(to_float(zr[i]));
+            ssq = fmaf(v, v, ssq);
+        }
     }
     const float inv = rsqrtf(block_sum(ssq, red) / (float)gsize + eps);
     T* dst = out + t * inner + c0;
+    if (pairs) {
+        for (int i = 2 * threadIdx.x; i < gsize; i += 2 * blockDim.x) {
+            const float2 yv = *reinterpret_cast<const float2*>(yr + i);
+            const float2 gv = *reinterpret_cast<const float2*>(gain + c0 + i);
+            const float v0 = yv.x * silu_f(to_float(zr[i])), v1 = yv.y * silu_f(to_float(zr[i + 1]));
+            dst[i] = from_float<T>((v0 * inv) * gv.x);
+            dst[i + 1] = from_float<T>((v1 * inv) * gv.y);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
         const float v = yr[i] * silu_f(to_float(zr[i]));
         dst[i] = from_float<T>((v * inv) * gain[c0 + i]);
@@ -233,8 +301,12 @@ LILY_API int lily_ssd_scan_max_state() { return 512; }
 LILY_API int lily_ssd_scan(const void* xbc, int channels, const void* proj, int proj_stride, int dt_col,
                            const float* dt_bias, const float* a_log, const float* d_skip, float* state,
                            size_t state_stride, float* y, const int* cu_seqlens, const int* slots, int requests,
-                           int heads, int pd, int n_state, int groups, int dtype, cudaStream_t stream) {
+                           int heads, int pd, int n_state, int groups, int dtype, const int* item_req,
+                           const int* item_start, const int* item_len, int mode, float* chunk_state, float* chunk_decay,
+                           cudaStream_t stream) {
     if (requests == 0) return 0;
+    LILY_REQUIRE(mode >= 0 && mode <= 2 && (mode == 0 || (chunk_state && chunk_decay && item_req && item_start && item_len)),
+                 "ssd_scan: mode %d needs item lists and a workspace", mode);
     LILY_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0, "ssd_scan: %d heads over %d groups", heads, groups);
     LILY_REQUIRE(n_state >= 1 && n_state <= 512 && pd >= 1, "ssd_scan: state %d (1 to 512), head size %d", n_state, pd);
     LILY_REQUIRE(requests <= 65535, "ssd_scan: %d requests", requests);
@@ -256,19 +328,33 @@ LILY_API int lily_ssd_scan(const void* xbc, int channels, const void* proj, int 
     // (a block is whole warps, so it has at least as many threads as a stage has tokens)
     const size_t smem = (size_t)tt * (2 * n_state + pb + 2) * sizeof(float);
     dim3 grid(heads, requests, (pd + pb - 1) / pb), block(cg * ns);
-#define GO(T, N, C)                                                                                                    \
-    launch_pdl(ssd_scan_kernel<T, N, C>, grid, block, smem, stream, (const T*)xbc, channels, (const T*)proj, proj_stride, \
+#define GO(T, N, C, E)                                                                                                 \
+    launch_pdl(ssd_scan_kernel<T, N, C, E>, grid, block, smem, stream, (const T*)xbc, channels, (const T*)proj, proj_stride, \
                dt_col, dt_bias, a_log, d_skip, state, state_stride, y, cu_seqlens, slots, heads, pd, n_state, groups, ns, \
-               pb, tt)
-#define GO_C(T, N) do { if (pc == 4) GO(T, N, 4); else if (pc == 2) GO(T, N, 2); else GO(T, N, 1); } while (0)
+               pb, tt, item_req, item_start, item_len, mode, chunk_state, chunk_decay)
+#define GO_E(T, N, C) do { if (mode == 1) GO(T, N, C, false); else GO(T, N, C, true); } while (0)
+#define GO_C(T, N) do { if (pc == 4) GO_E(T, N, 4); else if (pc == 2) GO_E(T, N, 2); else GO_E(T, N, 1); } while (0)
     if (dtype == kBF16) {
         if (npt == 4) GO_C(__nv_bfloat16, 4); else if (npt == 8) GO_C(__nv_bfloat16, 8); else GO_C(__nv_bfloat16, 16);
     } else {
         if (npt == 4) GO_C(float, 4); else if (npt == 8) GO_C(float, 8); else GO_C(float, 16);
     }
 #undef GO_C
+#undef GO_E
 #undef GO
     LILY_CHECK_LAUNCH("ssd_scan");
+    return 0;
+}
+
+LILY_API int lily_ssd_combine(float* state, size_t state_stride, const int* slots, float* chunk_state,
+                              const float* chunk_decay, const int* long_req, const int* long_first,
+                              const int* long_count, int portions, int heads, int per_head, cudaStream_t stream) {
+    if (portions == 0) return 0;
+    LILY_REQUIRE(portions <= 65535, "ssd_combine: %d portions", portions);
+    const size_t elements = (size_t)heads * per_head;
+    launch_pdl(ssd_combine_kernel, dim3((unsigned)((elements + 255) / 256), portions), dim3(256), 0, stream, state,
+               state_stride, slots, chunk_state, chunk_decay, long_req, long_first, long_count, heads, per_head);
+    LILY_CHECK_LAUNCH("ssd_combine");
     return 0;
 }
 

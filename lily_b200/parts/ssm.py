@@ -117,7 +117,13 @@ class SSD(Mixer):
         proj = ops.linear(x, self.w_in)                                       # [tokens, z | x | B | C | dt]
         xbc = ops.causal_conv_silu(proj, s.inner, s.channels, self.conv_w, self.conv_b, state, self.scan_floats,
                                    chunk_req, chunk_start, batch.cu_seqlens, batch.slots, chunk)
+        # long portions run as chunks side by side; what that takes is planned once a step for layers of one size
+        plan = batch.plan(("scan_plan", self.scan_floats),
+                          lambda b: ops.scan_plan(b.h_new_lens, b.token_ids.device, self.scan_floats))
+        need = ops.scan_workspace_floats(plan, s.heads, s.head_dim, s.state)
+        room = batch.workspace.floats("ssd_chunks", need) if need and batch.workspace is not None else None
         y = ops.ssd_scan(xbc, proj, s.inner + s.channels, self.dt_bias, self.a_log, self.d_skip, state,
-                         batch.cu_seqlens, batch.slots, batch.num_requests, s.heads, s.head_dim, s.state, s.groups)
+                         batch.cu_seqlens, batch.slots, batch.num_requests, s.heads, s.head_dim, s.state, s.groups,
+                         plan=plan, workspace=room)
         gated = ops.gated_group_rmsnorm(y, proj, self.gain, s.norm_groups, s.norm_eps)
         return ops.linear_auto(gated, self.w_out)

@@ -331,7 +331,16 @@ def causal_conv_silu(proj, col0, channels, weight, bias, state, state_off, chunk
     return out
 
 
-def ssd_scan(xbc, proj, dt_col, dt_bias, a_log, d_skip, state, cu_seqlens, slots, requests, heads, head_dim, n_state, groups):
+def scan_plan(new_lens, device, state_floats=0):
+    return None
+
+
+def scan_workspace_floats(plan, heads, head_dim, n_state):
+    return 0
+
+
+def ssd_scan(xbc, proj, dt_col, dt_bias, a_log, d_skip, state, cu_seqlens, slots, requests, heads, head_dim, n_state, groups,
+             plan=None, workspace=None):
     inner = heads * head_dim
     y = torch.empty((xbc.shape[0], inner), dtype=torch.float32, device=xbc.device)
     per = heads // groups

@@ -209,3 +209,22 @@ def test_replay_tool_in_every_cutting(dtype):
         for i, expect in enumerate(t.expect):
             want = torch.stack([plain[k][pos] for k, pos in expect])
             close(rows[i], want, dtype, f"step {i}")
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_a_long_prompt_whole_and_cut(device):
+    """700 tokens: portions long enough for the scan to run them as chunks side by side on the GPU, whole and cut at
+    odd places, beside a short request in the same step."""
+    cfg = zm.WIDE
+    with tempfile.TemporaryDirectory() as tmp:
+        weights = zm.make_weights(cfg, 14)
+        path = zm.write_model_dir(tmp + "/m", cfg, weights)
+        ids, other = zm.tokens(700, cfg["vocab"], 6), zm.tokens(30, cfg["vocab"], 7)
+        for dtype in dtypes(device, cfg):
+            want, want_other = plain_logits(cfg, weights, ids, dtype), plain_logits(cfg, weights, other, dtype)
+            runner = runner_for(path, device, dtype, max_tokens=1024, page_size=64)
+            close(run_whole(runner, ids), want, dtype, "whole")
+            close(run_portions(runner, ids, [333, 2, 1, 364]), want, dtype, "portions")
+            got = run_mixed(runner, {"a": ids, "b": other}, [{"a": 450, "b": 29}, {"a": 250, "b": 1}])
+            close(got["a"], want, dtype, "beside a short request")
+            close(got["b"], want_other, dtype, "the short request")

@@ -133,7 +133,7 @@ def test_convolution_carries_its_inputs(device, taps):
 def test_scan_carries_its_state(device, heads, pd, n_state, groups):
     ops = ops_for(device)
     g = torch.Generator().manual_seed(n_state)
-    t = 150
+    t = 470                     # portions past ``ops.SCAN_DIRECT`` tokens run as chunks side by side on the GPU
     inner = heads * pd
     xbc = torch.randn(t, inner + 2 * groups * n_state, generator=g)
     proj = torch.randn(t, 3 + heads, generator=g)
@@ -144,14 +144,15 @@ def test_scan_carries_its_state(device, heads, pd, n_state, groups):
     want = pz.ssd_scan(xbc[:, :inner].double().view(t, heads, pd), dt, -torch.exp(a_log.double()),
                        xbc[:, inner:inner + groups * n_state].double().view(t, groups, n_state),
                        xbc[:, inner + groups * n_state:].double().view(t, groups, n_state), d_skip.double()).float().view(t, inner)
-    for cuts in ([t], [100] + [1] * 50, [1, 2, 17, 2, 1, 1, 40, 3, 83]):
+    for cuts in ([t], [420] + [1] * 50, [1, 2, 17, 2, 1, 1, 40, 3, 193, 210]):
         state = torch.zeros(4, inner * n_state + 9, device=device)
         got, done = [], 0
         for n in cuts:
             rows_x = torch.cat([xbc[:3], xbc[done:done + n]]).to(device)          # a bystander's three tokens first
             rows_p = torch.cat([proj[:3], proj[done:done + n]]).to(device)
             y = ops.ssd_scan(rows_x, rows_p, 3, dt_bias.to(device), a_log.to(device), d_skip.to(device), state,
-                             i32([0, 3, 3 + n], device), i32([1, 3], device), 2, heads, pd, n_state, groups)
+                             i32([0, 3, 3 + n], device), i32([1, 3], device), 2, heads, pd, n_state, groups,
+                             plan=ops.scan_plan([3, n], device, inner * n_state))
             got.append(y[3:].float().cpu())
             done += n
         scale = max(1.0, float(want.abs().max()))
