@@ -86,9 +86,8 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
 // ---------------------------------------------------------------------------- selective scan
 
 // grid (heads, requests, ceil(head_dim / pb)), block (pb / PC) * ns threads: `ns` neighbouring lanes share PC
-// neighbouring value columns of the head's state and hold every ns-th of their `n_state` entries in registers (NPT
-// a column: PC * NPT numbers a thread, so that one B and one C entry read from shared memory serve 2 * PC
-// multiply-adds); the tokens of the request run one after another, staged `tt` at a time in shared memory (B and C
+// neighbouring value columns of the head's state and hold a run of NPT of their `n_state` entries each in registers
+// (PC * NPT numbers a thread, so that one B and one C entry read from shared memory serve 2 * PC multiply-adds); the tokens of the request run one after another, staged `tt` at a time in shared memory (B and C
 // of the head's group, the head's x, step sizes and decays).
 //
 // A work item (blockIdx.y) is a run of consecutive new tokens of one request.  Without item lists it is a request's
@@ -98,25 +97,31 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
 // S <- decay_c S + state_c, leaving in the workspace the state each chunk starts from and in the slot the last one;
 // mode 2 runs each chunk again from that state and writes the outputs.
 template <typename T, int NPT, int PC, bool EMIT>
-__global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ proj, int proj_stride,
-                                int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
-                                const float* __restrict__ d_skip, float* __restrict__ state, size_t state_stride,
-                                float* __restrict__ y, const int* __restrict__ cu_seqlens,
-                                const int* __restrict__ slots, int heads, int pd, int n_state, int groups, int ns,
-                                int pb, int tt, const int* __restrict__ item_req, const int* __restrict__ item_start,
-                                const int* __restrict__ item_len, int mode, float* __restrict__ chunk_state,
-                                float* __restrict__ chunk_decay) {
-    extern __shared__ float smem[];
+__global__ void __launch_bounds__(256, 2)
+ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ proj, int proj_stride,
+                int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                const float* __restrict__ d_skip, float* __restrict__ state, size_t state_stride,
+                float* __restrict__ y, const int* __restrict__ cu_seqlens,
+                const int* __restrict__ slots, int heads, int pd, int n_state, int groups, int ns,
+                int pb, int tt, const int* __restrict__ item_req, const int* __restrict__ item_start,
+                const int* __restrict__ item_len, int mode, float* __restrict__ chunk_state,
+                float* __restrict__ chunk_decay) {
+    extern __shared__ __align__(16) float smem[];
     pdl_enter_small();
+    // Lane j of the ns lanes that share PC columns holds entries [j * NPT, (j + 1) * NPT) of each column's state.  In
+    // shared memory a token's B (and C) is laid out lane by lane in rows of NPT + 4, so that the lanes' 16-byte reads
+    // fall into different banks; entries past n_state are zero there and leave their (zero) state entries alone.
+    constexpr int ROW = NPT + 4;
     const int h = blockIdx.x, item = blockIdx.y, p0 = blockIdx.z * pb;
     const int r = item_req ? item_req[item] : item;
     const int tid = threadIdx.x, j = tid % ns, pl = (tid / ns) * PC, p = p0 + pl;     // this thread's first column
     const int tok0 = cu_seqlens[r] + (item_start ? item_start[item] : 0);
     const int len = item_len ? item_len[item] : cu_seqlens[r + 1] - cu_seqlens[r];
     if (len <= 0) return;
-    float* Bs = smem;                        // [tt][n_state]
-    float* Cs = Bs + (size_t)tt * n_state;   // [tt][n_state]
-    float* xs = Cs + (size_t)tt * n_state;   // [tt][pb]
+    const int padded = ns * NPT, row = ns * ROW;
+    float* Bs = smem;                        // [tt][ns][ROW]
+    float* Cs = Bs + (size_t)tt * row;       // [tt][ns][ROW]
+    float* xs = Cs + (size_t)tt * row;       // [tt][pb]
     float* dts = xs + (size_t)tt * pb;       // [tt]
     float* das = dts + tt;                   // [tt]
     const int inner = heads * pd;
@@ -129,7 +134,7 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
     for (int c = 0; c < PC; ++c) {
 #pragma unroll
         for (int i = 0; i < NPT; ++i) {
-            const int n = i * ns + j;
+            const int n = j * NPT + i;
             S[c][i] = (mode != 1 && p + c < pd && n < n_state) ? st[(size_t)(p + c) * n_state + n] : 0.f;
         }
     }
@@ -138,15 +143,16 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
     for (int t0 = 0; t0 < len; t0 += tt) {
         const int now = min(tt, len - t0);
         __syncthreads();
-        for (int idx = tid; idx < now * n_state; idx += blockDim.x) {
-            const int ti = idx / n_state, n = idx - ti * n_state;
-            const T* row = xbc + (size_t)(tok0 + t0 + ti) * channels;
-            Bs[ti * n_state + n] = to_float(row[bcol + n]);
-            Cs[ti * n_state + n] = to_float(row[ccol + n]);
-        }
-        for (int idx = tid; idx < now * pb; idx += blockDim.x) {
-            const int ti = idx / pb, q = idx - ti * pb;
-            xs[ti * pb + q] = p0 + q < pd ? to_float(xbc[(size_t)(tok0 + t0 + ti) * channels + h * pd + p0 + q]) : 0.f;
+#pragma unroll 4
+        for (int ti = 0; ti < now; ++ti) {
+            const T* src = xbc + (size_t)(tok0 + t0 + ti) * channels;
+            for (int n = tid; n < padded; n += blockDim.x) {
+                const int at = ti * row + (n / NPT) * ROW + (n % NPT);
+                Bs[at] = n < n_state ? to_float(src[bcol + n]) : 0.f;
+                Cs[at] = n < n_state ? to_float(src[ccol + n]) : 0.f;
+            }
+            for (int q = tid; q < pb; q += blockDim.x)
+                xs[ti * pb + q] = p0 + q < pd ? to_float(src[h * pd + p0 + q]) : 0.f;
         }
         if (tid < now) {
             const float dtv = softplus_f(to_float(proj[(size_t)(tok0 + t0 + tid) * proj_stride + dt_col + h]) + bias);
@@ -157,8 +163,8 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
         for (int ti = 0; ti < now; ++ti) {
             const float da = das[ti], dtv = dts[ti];
             decayed *= da;
-            const float* bt = Bs + ti * n_state;
-            const float* ct = Cs + ti * n_state;
+            const float4* b4 = reinterpret_cast<const float4*>(Bs + ti * row + j * ROW);
+            const float4* c4 = reinterpret_cast<const float4*>(Cs + ti * row + j * ROW);
             float xv[PC], coef[PC], acc[PC];
 #pragma unroll
             for (int c = 0; c < PC; ++c) {
@@ -167,14 +173,15 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
                 acc[c] = 0.f;
             }
 #pragma unroll
-            for (int i = 0; i < NPT; ++i) {
-                const int n = i * ns + j;
-                if (n < n_state) {
-                    const float bn = bt[n], cn = ct[n];
+            for (int q = 0; q < NPT / 4; ++q) {
+                const float4 bv = b4[q], cv = c4[q];
+                const float bb[4] = {bv.x, bv.y, bv.z, bv.w}, cc[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
 #pragma unroll
                     for (int c = 0; c < PC; ++c) {
-                        S[c][i] = fmaf(da, S[c][i], coef[c] * bn);
-                        if (EMIT) acc[c] = fmaf(S[c][i], cn, acc[c]);
+                        S[c][4 * q + e] = fmaf(da, S[c][4 * q + e], coef[c] * bb[e]);
+                        if (EMIT) acc[c] = fmaf(S[c][4 * q + e], cc[e], acc[c]);
                     }
                 }
             }
@@ -192,7 +199,7 @@ __global__ void ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T
     for (int c = 0; c < PC; ++c) {
 #pragma unroll
         for (int i = 0; i < NPT; ++i) {
-            const int n = i * ns + j;
+            const int n = j * NPT + i;
             if (p + c < pd && n < n_state) st[(size_t)(p + c) * n_state + n] = S[c][i];
         }
     }
@@ -323,10 +330,11 @@ LILY_API int lily_ssd_scan(const void* xbc, int channels, const void* proj, int 
     while (cg * ns > 256) cg = (cg + 1) / 2;
     cg = (cg + lanes_cols - 1) / lanes_cols * lanes_cols;    // whole warps
     const int pb = cg * pc;
+    const int row = ns * (npt + 4);                      // a token's B (or C) in shared memory, padded lane by lane
     int tt = 16;
-    while (tt > 1 && (size_t)tt * (2 * n_state + pb + 2) * sizeof(float) > 40 * 1024) tt >>= 1;
+    while (tt > 1 && (size_t)tt * (2 * row + pb + 2) * sizeof(float) > 40 * 1024) tt >>= 1;
     // (a block is whole warps, so it has at least as many threads as a stage has tokens)
-    const size_t smem = (size_t)tt * (2 * n_state + pb + 2) * sizeof(float);
+    const size_t smem = (size_t)tt * (2 * row + pb + 2) * sizeof(float);
     dim3 grid(heads, requests, (pd + pb - 1) / pb), block(cg * ns);
 #define GO(T, N, C, E)                                                                                                 \
     launch_pdl(ssd_scan_kernel<T, N, C, E>, grid, block, smem, stream, (const T*)xbc, channels, (const T*)proj, proj_stride, \
