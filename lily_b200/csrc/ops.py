@@ -47,7 +47,7 @@ _SIGNATURES = {
     "lily_normed_mean": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _sz, _vp, _i, _i, _f, _f, _vp],
     "lily_causal_conv_silu": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _vp],
     "lily_ssd_scan": [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp,
-                      _i, _vp, _vp, _vp],
+                      _i, _vp, _vp, _i, _vp],
     "lily_ssd_combine": [_vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lily_gated_group_rmsnorm": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -826,6 +826,7 @@ class ScanPlan:
     long_first: Optional[torch.Tensor] = None
     long_count: Optional[torch.Tensor] = None
     num_long: int = 0
+    chunk: int = 0                           # the longest chunk, in tokens
 
 
 def scan_plan(new_lens: Sequence[int], device, state_floats: int = 0) -> ScanPlan:
@@ -836,7 +837,7 @@ def scan_plan(new_lens: Sequence[int], device, state_floats: int = 0) -> ScanPla
     if not longs:
         return ScanPlan(None, len(new_lens))
     chunk = SCAN_CHUNK
-    while state_floats and sum(-(-new_lens[r] // chunk) for r in longs) * state_floats * 4 > SCAN_WORKSPACE:
+    while chunk < 1024 and state_floats and sum(-(-new_lens[r] // chunk) for r in longs) * state_floats * 4 > SCAN_WORKSPACE:
         chunk *= 2
     direct = [r for r, n in enumerate(new_lens) if n <= SCAN_DIRECT]
     creq, cstart, clen, lfirst, lcount = [], [], [], [], []
@@ -851,7 +852,8 @@ def scan_plan(new_lens: Sequence[int], device, state_floats: int = 0) -> ScanPla
     dev = torch.tensor(flat, dtype=torch.int32).to(device, non_blocking=True)
     sizes = [len(direct)] + [len(creq)] * 3 + [len(longs)] * 3
     parts = torch.split(dev, sizes)
-    return ScanPlan(parts[0], len(direct), parts[1], parts[2], parts[3], len(creq), parts[4], parts[5], parts[6], len(longs))
+    return ScanPlan(parts[0], len(direct), parts[1], parts[2], parts[3], len(creq), parts[4], parts[5], parts[6], len(longs),
+                    chunk)
 
 
 def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
@@ -879,10 +881,10 @@ def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.
               state.shape[1], _p(y), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"))
     sizes = (heads, head_dim, n_state, groups, _dt(xbc))
     if plan is None or plan.direct is None:
-        _call("lily_ssd_scan", *common, int(requests), *sizes, None, None, None, 0, None, None, _stream())
+        _call("lily_ssd_scan", *common, int(requests), *sizes, None, None, None, 0, None, None, 0, _stream())
         return y
     if plan.num_direct:
-        _call("lily_ssd_scan", *common, plan.num_direct, *sizes, _p(plan.direct), None, None, 0, None, None, _stream())
+        _call("lily_ssd_scan", *common, plan.num_direct, *sizes, _p(plan.direct), None, None, 0, None, None, 0, _stream())
     need = scan_workspace_floats(plan, heads, head_dim, n_state)
     if workspace is None:
         workspace = torch.empty(need, dtype=torch.float32, device=xbc.device)
@@ -890,10 +892,10 @@ def ssd_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.
         raise KernelError(f"ssd_scan: a float32 workspace of {need} entries needed")
     chunk_state, chunk_decay = workspace, workspace[plan.num_chunks * inner * n_state:]
     items = (_p(plan.chunk_req), _p(plan.chunk_start), _p(plan.chunk_len))
-    _call("lily_ssd_scan", *common, plan.num_chunks, *sizes, *items, 1, _p(chunk_state), _p(chunk_decay), _stream())
+    _call("lily_ssd_scan", *common, plan.num_chunks, *sizes, *items, 1, _p(chunk_state), _p(chunk_decay), plan.chunk, _stream())
     _call("lily_ssd_combine", _p(state), state.shape[1], _i32(slots, "slots"), _p(chunk_state), _p(chunk_decay),
           _p(plan.long_req), _p(plan.long_first), _p(plan.long_count), plan.num_long, heads, head_dim * n_state, _stream())
-    _call("lily_ssd_scan", *common, plan.num_chunks, *sizes, *items, 2, _p(chunk_state), _p(chunk_decay), _stream())
+    _call("lily_ssd_scan", *common, plan.num_chunks, *sizes, *items, 2, _p(chunk_state), _p(chunk_decay), plan.chunk, _stream())
     return y
 
 

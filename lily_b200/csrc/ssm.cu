@@ -16,6 +16,12 @@
 namespace lily {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+
+__device__ __forceinline__ void copy16_async(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src));
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void copies_wait_all_but_one() { asm volatile("cp.async.wait_group 1;\n" ::); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
 // ---------------------------------------------------------------------------- causal convolution + SiLU
@@ -93,7 +99,9 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
 // A work item (blockIdx.y) is a run of consecutive new tokens of one request.  Without item lists it is a request's
 // whole portion, from the state in the request's slot to the state in the request's slot (mode 0).  A long portion
 // is cut into chunks that run side by side: mode 1 starts each chunk from zero and leaves the chunk's own state and
-// the product of its decays in a workspace (EMIT false: no outputs); a combine kernel then walks the chunks in order,
+// the product of its decays in a workspace (EMIT false: no outputs, and no recurrence either: the chunk's state is
+// the sum over its tokens of w_t B_t x_t^T with w_t = dt_t times the decays of the tokens after t, which the block
+// works out first, so that a state entry costs one multiply-add a token); a combine kernel then walks the chunks in order,
 // S <- decay_c S + state_c, leaving in the workspace the state each chunk starts from and in the slot the last one;
 // mode 2 runs each chunk again from that state and writes the outputs.
 template <typename T, int NPT, int PC, bool EMIT>
@@ -105,7 +113,7 @@ ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
                 const int* __restrict__ slots, int heads, int pd, int n_state, int groups, int ns,
                 int pb, int tt, const int* __restrict__ item_req, const int* __restrict__ item_start,
                 const int* __restrict__ item_len, int mode, float* __restrict__ chunk_state,
-                float* __restrict__ chunk_decay) {
+                float* __restrict__ chunk_decay, int ahead, int max_len) {
     extern __shared__ __align__(16) float smem[];
     pdl_enter_small();
     // Lane j of the ns lanes that share PC columns holds entries [j * NPT, (j + 1) * NPT) of each column's state.  In
@@ -124,9 +132,28 @@ ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
     float* xs = Cs + (size_t)tt * row;       // [tt][pb]
     float* dts = xs + (size_t)tt * pb;       // [tt]
     float* das = dts + tt;                   // [tt]
+    float* wts = das + tt;                   // mode 1: [max_len] weights w_t, then [max_len] decays
     const int inner = heads * pd;
     const int g = h / (heads / groups);
     const int bcol = inner + g * n_state, ccol = inner + (groups + g) * n_state;
+    // `ahead`: the next stage's B, C and x rows are copied as they are (16-byte pieces, asynchronously) into one of two
+    // raw buffers while this stage is worked on, and spread into the padded float32 layout when their turn comes
+    const int ex = 16 / (int)sizeof(T);                                   // elements a piece
+    const int pieces_b = n_state / ex, pieces_x = pb / ex, pieces = 2 * pieces_b + pieces_x;     // of one token
+    T* raw = reinterpret_cast<T*>(wts + (EMIT ? 0 : 2 * max_len));        // [2][tt][pieces * ex]
+    float dt_ahead = 0.f;
+    auto ask = [&](int t0, int buf) {
+        const int now = min(tt, len - t0);
+        for (int q = tid; q < now * pieces; q += blockDim.x) {
+            const int ti = q / pieces, k = q - ti * pieces;
+            const T* src = xbc + (size_t)(tok0 + t0 + ti) * channels;
+            const T* from = k < pieces_b ? src + bcol + k * ex
+                          : (k < 2 * pieces_b ? src + ccol + (k - pieces_b) * ex : src + h * pd + p0 + (k - 2 * pieces_b) * ex);
+            if (k < 2 * pieces_b || p0 + (k - 2 * pieces_b) * ex < pd)
+                copy16_async(raw + ((size_t)(buf * tt + ti) * pieces + k) * ex, from);
+        }
+        if (EMIT && tid < now) dt_ahead = to_float(proj[(size_t)(tok0 + t0 + tid) * proj_stride + dt_col + h]);
+    };
     float* st = (mode == 0 ? state + (size_t)slots[r] * state_stride : chunk_state + (size_t)item * heads * pd * n_state) +
                 (size_t)h * pd * n_state;
     float S[PC][NPT];
@@ -140,8 +167,61 @@ ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
     }
     const float A = -expf(a_log[h]), bias = dt_bias[h], D = d_skip[h];
     float decayed = 1.f;                     // the product of the item's decays
+    if (!EMIT) {
+        float* dec = wts + len;
+        for (int t = tid; t < len; t += blockDim.x) {
+            const float dtv = softplus_f(to_float(proj[(size_t)(tok0 + t) * proj_stride + dt_col + h]) + bias);
+            wts[t] = dtv;
+            dec[t] = expf(A * dtv);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float after = 1.f;               // the decays of the tokens behind t
+            for (int t = len - 1; t >= 0; --t) {
+                wts[t] *= after;
+                after *= dec[t];
+            }
+            dec[0] = after;
+        }
+        __syncthreads();
+        decayed = dec[0];
+    }
+    if (ahead) {
+        for (int q = tid; q < 2 * tt * row; q += blockDim.x) Bs[q] = 0.f;        // entries past n_state stay zero
+        ask(0, 0);
+        copies_commit();
+    }
     for (int t0 = 0; t0 < len; t0 += tt) {
         const int now = min(tt, len - t0);
+        if (ahead) {
+            const int buf = (t0 / tt) & 1;
+            const float dt_now = dt_ahead;
+            __syncthreads();                                   // the stage before has been worked through
+            if (t0 + tt < len) ask(t0 + tt, buf ^ 1);
+            copies_commit();
+            copies_wait_all_but_one();
+            __syncthreads();                                   // this stage's pieces have landed, for every thread
+            for (int q = tid; q < now * pieces; q += blockDim.x) {
+                const int ti = q / pieces, k = q - ti * pieces;
+                const T* at = raw + ((size_t)(buf * tt + ti) * pieces + k) * ex;
+                float* to;
+                int first;
+                if (k < 2 * pieces_b) {
+                    first = (k < pieces_b ? k : k - pieces_b) * ex;
+                    to = (k < pieces_b ? Bs : Cs) + ti * row;
+                    for (int e = 0; e < ex; ++e) to[((first + e) / NPT) * ROW + (first + e) % NPT] = to_float(at[e]);
+                } else {
+                    first = (k - 2 * pieces_b) * ex;
+                    for (int e = 0; e < ex; ++e) xs[ti * pb + first + e] = p0 + first + e < pd ? to_float(at[e]) : 0.f;
+                }
+            }
+            if (EMIT && tid < now) {
+                const float dtv = softplus_f(dt_now + bias);
+                dts[tid] = dtv;
+                das[tid] = expf(A * dtv);
+            }
+            __syncthreads();
+        } else {
         __syncthreads();
 #pragma unroll 4
         for (int ti = 0; ti < now; ++ti) {
@@ -154,15 +234,15 @@ ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
             for (int q = tid; q < pb; q += blockDim.x)
                 xs[ti * pb + q] = p0 + q < pd ? to_float(src[h * pd + p0 + q]) : 0.f;
         }
-        if (tid < now) {
+        if (EMIT && tid < now) {
             const float dtv = softplus_f(to_float(proj[(size_t)(tok0 + t0 + tid) * proj_stride + dt_col + h]) + bias);
             dts[tid] = dtv;
             das[tid] = expf(A * dtv);
         }
         __syncthreads();
+        }
         for (int ti = 0; ti < now; ++ti) {
-            const float da = das[ti], dtv = dts[ti];
-            decayed *= da;
+            const float da = EMIT ? das[ti] : 1.f, dtv = EMIT ? dts[ti] : wts[t0 + ti];
             const float4* b4 = reinterpret_cast<const float4*>(Bs + ti * row + j * ROW);
             const float4* c4 = reinterpret_cast<const float4*>(Cs + ti * row + j * ROW);
             float xv[PC], coef[PC], acc[PC];
@@ -180,15 +260,36 @@ ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
                 for (int e = 0; e < 4; ++e) {
 #pragma unroll
                     for (int c = 0; c < PC; ++c) {
-                        S[c][4 * q + e] = fmaf(da, S[c][4 * q + e], coef[c] * bb[e]);
-                        if (EMIT) acc[c] = fmaf(S[c][4 * q + e], cc[e], acc[c]);
+                        if (EMIT) {
+                            S[c][4 * q + e] = fmaf(da, S[c][4 * q + e], coef[c] * bb[e]);
+                            acc[c] = fmaf(S[c][4 * q + e], cc[e], acc[c]);
+                        } else {
+                            S[c][4 * q + e] = fmaf(coef[c], bb[e], S[c][4 * q + e]);
+                        }
                     }
                 }
             }
-            if (EMIT) {
+            if (EMIT && PC == 4 && ns >= 4) {
+                // four sums over ns lanes in 2 + 1 + log2(ns / 4) exchanges: partners swap halves, then quarters, and
+                // lane j < 4 ends with the sum of column 2 (j & 1) + (j >> 1)
+                const bool odd = j & 1, upper = j & 2;
+                float k0 = odd ? acc[PC - 2] : acc[0], k1 = odd ? acc[PC - 1] : acc[1];
+                k0 += __shfl_xor_sync(0xffffffffu, odd ? acc[0] : acc[PC - 2], 1);
+                k1 += __shfl_xor_sync(0xffffffffu, odd ? acc[1] : acc[PC - 1], 1);
+                float k = upper ? k1 : k0;
+                k += __shfl_xor_sync(0xffffffffu, upper ? k0 : k1, 2);
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1)
+                    if (o < ns) k += __shfl_xor_sync(0xffffffffu, k, o);
+                const int col = 2 * (j & 1) + ((j >> 1) & 1);
+                const float xcol = col == 0 ? xv[0] : (col == 1 ? xv[1] : (col == 2 ? xv[PC - 2] : xv[PC - 1]));
+                if (j < 4 && p + col < pd) y[(size_t)(tok0 + t0 + ti) * inner + h * pd + p + col] = fmaf(D, xcol, k);
+            } else if (EMIT) {
 #pragma unroll
                 for (int c = 0; c < PC; ++c) {
-                    for (int o = ns >> 1; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1)
+                        if (o < ns) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
                     if (j == 0 && p + c < pd) y[(size_t)(tok0 + t0 + ti) * inner + h * pd + p + c] = fmaf(D, xv[c], acc[c]);
                 }
             }
@@ -310,7 +411,7 @@ LILY_API int lily_ssd_scan(const void* xbc, int channels, const void* proj, int 
                            size_t state_stride, float* y, const int* cu_seqlens, const int* slots, int requests,
                            int heads, int pd, int n_state, int groups, int dtype, const int* item_req,
                            const int* item_start, const int* item_len, int mode, float* chunk_state, float* chunk_decay,
-                           cudaStream_t stream) {
+                           int max_item_len, cudaStream_t stream) {
     if (requests == 0) return 0;
     LILY_REQUIRE(mode >= 0 && mode <= 2 && (mode == 0 || (chunk_state && chunk_decay && item_req && item_start && item_len)),
                  "ssd_scan: mode %d needs item lists and a workspace", mode);
@@ -332,14 +433,31 @@ LILY_API int lily_ssd_scan(const void* xbc, int channels, const void* proj, int 
     const int pb = cg * pc;
     const int row = ns * (npt + 4);                      // a token's B (or C) in shared memory, padded lane by lane
     int tt = 16;
-    while (tt > 1 && (size_t)tt * (2 * row + pb + 2) * sizeof(float) > 40 * 1024) tt >>= 1;
+    while (tt > 1 && (size_t)tt * (2 * row + pb + 2) * sizeof(float) > 36 * 1024) tt >>= 1;
     // (a block is whole warps, so it has at least as many threads as a stage has tokens)
-    const size_t smem = (size_t)tt * (2 * row + pb + 2) * sizeof(float);
+    LILY_REQUIRE(mode != 1 || (max_item_len >= 1 && max_item_len <= 1024), "ssd_scan: chunks of up to %d tokens (1 to 1024)", max_item_len);
+    const int max_len = mode == 1 ? max_item_len : 0;
+    // rows are copied ahead where every piece of 16 bytes is whole and aligned (and the items are longer than a stage)
+    const size_t item = dtype == kBF16 ? 2 : 4;
+    const int ahead = ((uintptr_t)xbc % 16 == 0 && (channels * item) % 16 == 0 && (heads * pd * item) % 16 == 0 &&
+                       (n_state * item) % 16 == 0 && (pd * item) % 16 == 0 && (pb * item) % 16 == 0 && tt % 2 == 0 && (item_len != nullptr)) ? 1 : 0;
+    const size_t raw_bytes = ahead ? 2 * (size_t)tt * (2 * n_state + pb) * item : 0;
+    const size_t smem = ((size_t)tt * (2 * row + pb + 2) + 2 * (size_t)max_len) * sizeof(float) + raw_bytes;
+    LILY_REQUIRE(smem <= 200 * 1024, "ssd_scan: %zu bytes of shared memory", smem);
     dim3 grid(heads, requests, (pd + pb - 1) / pb), block(cg * ns);
 #define GO(T, N, C, E)                                                                                                 \
-    launch_pdl(ssd_scan_kernel<T, N, C, E>, grid, block, smem, stream, (const T*)xbc, channels, (const T*)proj, proj_stride, \
-               dt_col, dt_bias, a_log, d_skip, state, state_stride, y, cu_seqlens, slots, heads, pd, n_state, groups, ns, \
-               pb, tt, item_req, item_start, item_len, mode, chunk_state, chunk_decay)
+    do {                                                                                                               \
+        auto kern = ssd_scan_kernel<T, N, C, E>;                                                                       \
+        static size_t granted = 48 * 1024;      /* raised once per kernel, never while a graph is captured */           \
+        if (smem > granted) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+            if (e != cudaSuccess) { set_error("ssd_scan: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return 2; } \
+            granted = smem;                                                                                            \
+        }                                                                                                              \
+        launch_pdl(kern, grid, block, smem, stream, (const T*)xbc, channels, (const T*)proj, proj_stride,              \
+                   dt_col, dt_bias, a_log, d_skip, state, state_stride, y, cu_seqlens, slots, heads, pd, n_state, groups, ns, \
+                   pb, tt, item_req, item_start, item_len, mode, chunk_state, chunk_decay, ahead, max_len);            \
+    } while (0)
 #define GO_E(T, N, C) do { if (mode == 1) GO(T, N, C, false); else GO(T, N, C, true); } while (0)
 #define GO_C(T, N) do { if (pc == 4) GO_E(T, N, 4); else if (pc == 2) GO_E(T, N, 2); else GO_E(T, N, 1); } while (0)
     if (dtype == kBF16) {
