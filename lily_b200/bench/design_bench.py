@@ -154,8 +154,11 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
         vecs = [rnd(z["s_heads"]) - 2 for _ in range(3)]
         scan_flops = 6.0 * n * inner * z["state"]
         scan_bytes = n * (channels * 2 + inner * 4) + 2 * reqs * inner * z["state"] * 4
+        plan = ops.scan_plan([per] * reqs, dev, inner * z["state"])            # long portions run as chunks, as in the model
+        room = torch.empty(max(1, ops.scan_workspace_floats(plan, z["s_heads"], z["s_head"], z["state"])), device=dev)
         add("ssd_scan", "attention", [lambda x=x, p=p, s=s: ops.ssd_scan(x, p, inner + channels, vecs[0], vecs[1], vecs[2], s, cu, slots, reqs,
-                                                                          z["s_heads"], z["s_head"], z["state"], z["groups"])
+                                                                          z["s_heads"], z["s_head"], z["state"], z["groups"],
+                                                                          plan=plan, workspace=room)
                                       for x, p, s in zip(xbcs, projs, states)],
             scan_bytes, scan_flops, fp32_tflops, shape=label)
         ys = [rnd(n, inner) for _ in range(copies)]

@@ -113,7 +113,7 @@ ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
                 const int* __restrict__ slots, int heads, int pd, int n_state, int groups, int ns,
                 int pb, int tt, const int* __restrict__ item_req, const int* __restrict__ item_start,
                 const int* __restrict__ item_len, int mode, float* __restrict__ chunk_state,
-                float* __restrict__ chunk_decay, int ahead, int max_len) {
+                float* __restrict__ chunk_decay, int ahead, int max_len, int wide) {
     extern __shared__ __align__(16) float smem[];
     pdl_enter_small();
     // Lane j of the ns lanes that share PC columns holds entries [j * NPT, (j + 1) * NPT) of each column's state.  In
@@ -157,12 +157,23 @@ ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
     float* st = (mode == 0 ? state + (size_t)slots[r] * state_stride : chunk_state + (size_t)item * heads * pd * n_state) +
                 (size_t)h * pd * n_state;
     float S[PC][NPT];
+    // 16-byte accesses to the state where its rows allow them (`wide`: n_state a multiple of four, aligned bases)
+    const bool whole_run = wide && (j + 1) * NPT <= n_state;
 #pragma unroll
     for (int c = 0; c < PC; ++c) {
+        if (whole_run && mode != 1 && p + c < pd) {
+            const float4* src4 = reinterpret_cast<const float4*>(st + (size_t)(p + c) * n_state + j * NPT);
 #pragma unroll
-        for (int i = 0; i < NPT; ++i) {
-            const int n = j * NPT + i;
-            S[c][i] = (mode != 1 && p + c < pd && n < n_state) ? st[(size_t)(p + c) * n_state + n] : 0.f;
+            for (int q = 0; q < NPT / 4; ++q) {
+                const float4 v = src4[q];
+                S[c][4 * q] = v.x; S[c][4 * q + 1] = v.y; S[c][4 * q + 2] = v.z; S[c][4 * q + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+                const int n = j * NPT + i;
+                S[c][i] = (mode != 1 && p + c < pd && n < n_state) ? st[(size_t)(p + c) * n_state + n] : 0.f;
+            }
         }
     }
     const float A = -expf(a_log[h]), bias = dt_bias[h], D = d_skip[h];
@@ -298,10 +309,16 @@ ssd_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
     if (mode == 2) return;
 #pragma unroll
     for (int c = 0; c < PC; ++c) {
+        if (whole_run && p + c < pd) {
+            float4* dst4 = reinterpret_cast<float4*>(st + (size_t)(p + c) * n_state + j * NPT);
 #pragma unroll
-        for (int i = 0; i < NPT; ++i) {
-            const int n = j * NPT + i;
-            if (p + c < pd && n < n_state) st[(size_t)(p + c) * n_state + n] = S[c][i];
+            for (int q = 0; q < NPT / 4; ++q) dst4[q] = make_float4(S[c][4 * q], S[c][4 * q + 1], S[c][4 * q + 2], S[c][4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+                const int n = j * NPT + i;
+                if (p + c < pd && n < n_state) st[(size_t)(p + c) * n_state + n] = S[c][i];
+            }
         }
     }
     if (mode == 1 && tid == 0 && blockIdx.z == 0) chunk_decay[(size_t)item * heads + h] = decayed;
@@ -441,6 +458,7 @@ LILY_API int lily_ssd_scan(const void* xbc, int channels, const void* proj, int 
     const size_t item = dtype == kBF16 ? 2 : 4;
     const int ahead = ((uintptr_t)xbc % 16 == 0 && (channels * item) % 16 == 0 && (heads * pd * item) % 16 == 0 &&
                        (n_state * item) % 16 == 0 && (pd * item) % 16 == 0 && (pb * item) % 16 == 0 && tt % 2 == 0 && (item_len != nullptr)) ? 1 : 0;
+    const int wide = (n_state % 4 == 0 && state_stride % 4 == 0 && (uintptr_t)state % 16 == 0 && (uintptr_t)chunk_state % 16 == 0) ? 1 : 0;
     const size_t raw_bytes = ahead ? 2 * (size_t)tt * (2 * n_state + pb) * item : 0;
     const size_t smem = ((size_t)tt * (2 * row + pb + 2) + 2 * (size_t)max_len) * sizeof(float) + raw_bytes;
     LILY_REQUIRE(smem <= 200 * 1024, "ssd_scan: %zu bytes of shared memory", smem);
@@ -456,7 +474,7 @@ LILY_API int lily_ssd_scan(const void* xbc, int channels, const void* proj, int 
         }                                                                                                              \
         launch_pdl(kern, grid, block, smem, stream, (const T*)xbc, channels, (const T*)proj, proj_stride,              \
                    dt_col, dt_bias, a_log, d_skip, state, state_stride, y, cu_seqlens, slots, heads, pd, n_state, groups, ns, \
-                   pb, tt, item_req, item_start, item_len, mode, chunk_state, chunk_decay, ahead, max_len);            \
+                   pb, tt, item_req, item_start, item_len, mode, chunk_state, chunk_decay, ahead, max_len, wide);      \
     } while (0)
 #define GO_E(T, N, C) do { if (mode == 1) GO(T, N, C, false); else GO(T, N, C, true); } while (0)
 #define GO_C(T, N) do { if (pc == 4) GO_E(T, N, 4); else if (pc == 2) GO_E(T, N, 2); else GO_E(T, N, 1); } while (0)
