@@ -99,8 +99,16 @@ struct Params {
     const int* tile_start;
     __nv_bfloat16* out;
     int bt_stride, tiles, nq, nkv, page_size, window;
-    float scale_log2;                     // softmax scale times log2(e)
+    float scale_log2;                     // softmax scale times log2(e) (log2(e) alone under a cap)
+    float cap, cap_in;                    // cap > 0: scores become cap * tanh(score * cap_in), cap_in = scale / cap
 };
+
+// The hardware's tanh (relative error about 2^-11; the weights are rounded to bfloat16 for the p.v product).
+__device__ __forceinline__ float tanh_fast(float v) {
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -435,6 +443,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int c = 0; c < COLS / 32; ++c) tmem_ld32(tmem + lane_addr + (uint32_t)(b * BKV + part * COLS + c * 32), s + c * 32);
             tmem_wait_ld();
+            if (p.cap > 0.f) {
+#pragma unroll
+                for (int c = 0; c < COLS; ++c) s[c] = p.cap * tanh_fast(s[c] * p.cap_in);
+            }
             FA_TOC(10 + (part & 1), row == 0);
             const int kb = (jt0 + j) * BKV + part * COLS;
             const bool need_mask = kb + COLS - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
@@ -787,6 +799,10 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 float s[32];
                 tmem_ld32(my_s + (uint32_t)(c * 32), s);
                 tmem_wait_ld();
+                if (p.cap > 0.f) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) s[e] = p.cap * tanh_fast(s[e] * p.cap_in);
+                }
                 if (need_mask) {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
@@ -833,6 +849,10 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 float s[32];
                 tmem_ld32(my_s + (uint32_t)(c * 32), s);
                 tmem_wait_ld();
+                if (p.cap > 0.f) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) s[e] = p.cap * tanh_fast(s[e] * p.cap_in);
+                }
                 if (need_mask) {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
@@ -965,7 +985,8 @@ LILY_API int lily_attention_tc_status() {
 LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out, const int* block_table, int bt_stride,
                                        const int* cu_seqlens, const int* prefix_lens, const int* tile_req,
                                        const int* tile_start, int tiles, int nq, int nkv, int d, int page_size, int window,
-                                       float scale, int tokens, int num_pages, int heads_per_block, cudaStream_t stream) {
+                                       float scale, int tokens, int num_pages, int heads_per_block, float softcap,
+                                       cudaStream_t stream) {
     if (tiles == 0) return 0;
     LILY_REQUIRE(lily_attention_prefill_tc_takes(d, page_size), "attention_prefill_tc: head size %d, page size %d (takes 64 or 128, and multiples of 64)",
                  d, page_size);
@@ -998,7 +1019,10 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
     fa::Params p{};
     p.block_table = block_table; p.cu_seqlens = cu_seqlens; p.prefix_lens = prefix_lens; p.tile_req = tile_req;
     p.tile_start = tile_start; p.out = (__nv_bfloat16*)out; p.bt_stride = bt_stride; p.tiles = tiles; p.nq = nq; p.nkv = nkv;
-    p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.page_size = page_size; p.window = window;
+    p.cap = softcap > 0.f ? softcap : 0.f;
+    p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
+    p.scale_log2 = (softcap > 0.f ? 1.f : scale) * 1.4426950408889634f;
     // two heads of a kv head a block when the group size is even and, unless the caller says which, when
     // that still leaves a block for every SM (short prompts fill the device better with a head a block)
     const int sms = sm_count();

@@ -39,7 +39,7 @@ _SIGNATURES = {
     "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp],
-    "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
+    "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _f, _vp],
     "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _vp],
     "lily_attention_decode_mma_fused": [_vp, _i, _sz, _i, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp,
                                         _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _vp],
@@ -471,11 +471,11 @@ def uses_tensor_cores(dtype: torch.dtype, d: int) -> bool:
 TC_ATTENTION_MIN_TOKENS = 128
 
 
-def uses_tcgen05_attention(dtype: torch.dtype, d: int, page_size: int, new_tokens: int, plain: bool = True) -> bool:
+def uses_tcgen05_attention(dtype: torch.dtype, d: int, page_size: int, new_tokens: int) -> bool:
     """Whether prefill attention of this precision, head size, page size and number of new tokens
-    runs on the tcgen05 kernel (bfloat16, head size 128 or 64, pages of a multiple of 64 positions, scores that
-    are only scaled: ``plain`` is False for soft-capped scores, which the mma.sync kernel takes)."""
-    return (plain and dtype == torch.bfloat16 and new_tokens >= TC_ATTENTION_MIN_TOKENS
+    runs on the tcgen05 kernel (bfloat16, head size 128 or 64, pages of a multiple of 64 positions; scores scaled
+    or soft-capped)."""
+    return (dtype == torch.bfloat16 and new_tokens >= TC_ATTENTION_MIN_TOKENS
             and bool(library().lily_attention_prefill_tc_takes(int(d), int(page_size))))
 
 
@@ -485,7 +485,7 @@ def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size:
     where it differs), page size, number of new tokens and kind of scores."""
     lib = library()
     same = dv is None or dv == d
-    if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens, plain=not softcap):
+    if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens):
         return int(lib.lily_attention_prefill_tc_rows())
     return int(lib.lily_attention_prefill_mma_rows() if same and uses_tensor_cores(dtype, d) else lib.lily_attention_prefill_simt_rows())
 
@@ -501,7 +501,7 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
                       tile_rows: Optional[int] = None, heads_per_block: int = 0, softcap: Optional[float] = None,
                       dv: Optional[int] = None) -> None:
     """Causal attention of each request's new tokens over its cached prefix and themselves.  ``softcap``: scores
-    become softcap * tanh(score * scale / softcap) before the softmax (mma.sync and CUDA-core kernels); ``dv``: the
+    become softcap * tanh(score * scale / softcap) before the softmax; ``dv``: the
     value head size where it differs from d (CUDA-core kernels; ``out`` is then [tokens, nq * dv]).
     ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)
     in steps of ``tile_rows`` (default: ``prefill_tile_rows(q.dtype, d)``), which also names the
@@ -519,13 +519,13 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
     tensor_cores = dv == d and uses_tensor_cores(q.dtype, d)
     base_rows = int(lib.lily_attention_prefill_mma_rows() if tensor_cores else lib.lily_attention_prefill_simt_rows())
     if tile_rows is not None and tile_rows != base_rows:
-        if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16 and dv == d and not cap
+        if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16 and dv == d
                 and lib.lily_attention_prefill_tc_takes(int(d), int(page_size))):
             raise KernelError(f"attention_prefill: no kernel with tiles of {tile_rows} rows for {q.dtype}, head size {d}, "
                               f"page size {page_size}")
         if not (q.is_contiguous() and out.is_contiguous() and kv_layer.is_contiguous()):
             raise KernelError("attention_prefill: the tcgen05 kernel takes contiguous q, out and cache")
-        _call("lily_attention_prefill_tc", *common, q.shape[0], kv_layer.shape[0], int(heads_per_block), _stream())
+        _call("lily_attention_prefill_tc", *common, q.shape[0], kv_layer.shape[0], int(heads_per_block), cap, _stream())
     elif tensor_cores:
         _call("lily_attention_prefill_mma", *common, cap, _stream())
     else:
