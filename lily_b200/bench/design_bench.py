@@ -135,6 +135,7 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
             row["flop_frac"] = round(flops / ms / 1e9 / (flop_peak or pk["bf16_tflops"]), 3)
             row["flop_peak"] = "fp32 fma" if flop_peak else "bf16 tensor"
         row["roofline_frac"] = max(row["hbm_frac"], row.get("flop_frac", 0.0))
+        row["bound"] = row.get("flop_peak", "hbm") if row.get("flop_frac", 0.0) > row["hbm_frac"] else "hbm"
         rows.append(row)
 
     for label, n, reqs in (("prefill", tokens, 1), ("decode", batch, batch)):
@@ -255,7 +256,8 @@ def main(argv=None) -> int:
                     print(name, k, entry[k], file=sys.stderr)
             for row in entry.get("kernels", []):
                 print(f"{name:6s} {row['kernel']:32s} {row['shape']:14s} {row['us']:10.2f} us  hbm {row['hbm_frac']:.3f}"
-                      + (f"  {row['flop_peak']} {row['flop_frac']:.3f}" if "flop_frac" in row else ""), file=sys.stderr)
+                      + (f"  {row['flop_peak']} {row['flop_frac']:.3f}" if "flop_frac" in row else "") + f"  ({row['bound']})",
+                      file=sys.stderr)
     print(json.dumps(out))
     return 0
 

@@ -353,7 +353,8 @@ __global__ void ssd_combine_kernel(float* __restrict__ state, size_t state_strid
 template <typename T>
 __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ z, int z_stride,
                                            const float* __restrict__ gain, T* __restrict__ out, int inner,
-                                           int gsize, float eps) {
+                                           int gsize, float eps, int stash) {
+    extern __shared__ float gated[];          // [gsize] when `stash`: the gated values, formed once
     __shared__ float red[33];
     pdl_enter_small();
     const size_t t = blockIdx.x;
@@ -367,28 +368,36 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
         for (int i = 2 * threadIdx.x; i < gsize; i += 2 * blockDim.x) {
             const float2 yv = *reinterpret_cast<const float2*>(yr + i);
             const float v0 = yv.x * silu_f(to_float(zr[i])), v1 = yv.y * silu_f(to_float(zr[i + 1]));
+            if (stash) *reinterpret_cast<float2*>(gated + i) = make_float2(v0, v1);
             ssq += v0 * v0 + v1 * v1;
         }
     } else {
         for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
             const float v = yr[i] * silu_f(to_float(zr[i]));
+            if (stash) gated[i] = v;
             ssq = fmaf(v, v, ssq);
         }
     }
-    const float inv = rsqrtf(block_sum(ssq, red) / (float)gsize + eps);
+    const float inv = rsqrtf(block_sum(ssq, red) / (float)gsize + eps);      // (its barriers also publish `gated`)
     T* dst = out + t * inner + c0;
     if (pairs) {
         for (int i = 2 * threadIdx.x; i < gsize; i += 2 * blockDim.x) {
-            const float2 yv = *reinterpret_cast<const float2*>(yr + i);
+            float v0, v1;
+            if (stash) {
+                const float2 v = *reinterpret_cast<const float2*>(gated + i);
+                v0 = v.x; v1 = v.y;
+            } else {
+                const float2 yv = *reinterpret_cast<const float2*>(yr + i);
+                v0 = yv.x * silu_f(to_float(zr[i])); v1 = yv.y * silu_f(to_float(zr[i + 1]));
+            }
             const float2 gv = *reinterpret_cast<const float2*>(gain + c0 + i);
-            const float v0 = yv.x * silu_f(to_float(zr[i])), v1 = yv.y * silu_f(to_float(zr[i + 1]));
             dst[i] = from_float<T>((v0 * inv) * gv.x);
             dst[i + 1] = from_float<T>((v1 * inv) * gv.y);
         }
         return;
     }
     for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
-        const float v = yr[i] * silu_f(to_float(zr[i]));
+        const float v = stash ? gated[i] : yr[i] * silu_f(to_float(zr[i]));
         dst[i] = from_float<T>((v * inv) * gain[c0 + i]);
     }
 }
@@ -508,12 +517,15 @@ LILY_API int lily_gated_group_rmsnorm(const float* y, const void* z, int z_strid
     LILY_REQUIRE(groups >= 1 && inner % groups == 0, "gated_group_rmsnorm: %d columns in %d groups", inner, groups);
     LILY_REQUIRE(groups <= 65535, "gated_group_rmsnorm: %d groups", groups);
     dim3 grid(tokens, groups), block(256);
+    const int gsize = inner / groups;
+    const int stash = gsize <= 10240;              // 40 KB of shared memory hold the group's gated values
+    const size_t smem = stash ? (size_t)gsize * sizeof(float) : 0;
     if (dtype == kBF16)
-        launch_pdl(gated_group_rmsnorm_kernel<__nv_bfloat16>, grid, block, 0, stream, y, (const __nv_bfloat16*)z, z_stride,
-                   gain, (__nv_bfloat16*)out, inner, inner / groups, eps);
+        launch_pdl(gated_group_rmsnorm_kernel<__nv_bfloat16>, grid, block, smem, stream, y, (const __nv_bfloat16*)z, z_stride,
+                   gain, (__nv_bfloat16*)out, inner, gsize, eps, stash);
     else
-        launch_pdl(gated_group_rmsnorm_kernel<float>, grid, block, 0, stream, y, (const float*)z, z_stride, gain,
-                   (float*)out, inner, inner / groups, eps);
+        launch_pdl(gated_group_rmsnorm_kernel<float>, grid, block, smem, stream, y, (const float*)z, z_stride, gain,
+                   (float*)out, inner, gsize, eps, stash);
     LILY_CHECK_LAUNCH("gated_group_rmsnorm");
     return 0;
 }

@@ -104,11 +104,12 @@ def test_one_key_that_stands_out(device, heads, kvh, d, dv, window, softcap):
 # ------------------------------------------------------------------ the state-space mixer's kernels
 
 @pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("width,col0", [(91, 13), (92, 12)])        # odd rows and offsets, and even ones
 @pytest.mark.parametrize("taps", [1, 2, 4, 7])
-def test_convolution_carries_its_inputs(device, taps):
+def test_convolution_carries_its_inputs(device, taps, width, col0):
     ops = ops_for(device)
     g = torch.Generator().manual_seed(taps)
-    t, width, col0, channels = 200, 91, 13, 70
+    t, channels = 200, 70
     proj = torch.randn(t, width, generator=g)
     w = torch.randn(channels, taps, generator=g) * 0.5
     b = torch.randn(channels, generator=g) * 0.2
