@@ -188,7 +188,11 @@ class ModelRunner:
                 free, total = torch.cuda.mem_get_info(self.device)
             else:
                 free = total = 1 << 30
-            pages = pool_pages_from_memory(groups, self.dtype, self.page_size, free, total,
+            # the state rows of the request slots (mixers with a recurrence) come out of the same memory
+            slots = int(args.max_running_requests or 256) + 1
+            state_bytes = slots * sum(torch.empty((), dtype=n.dtype).element_size() * int(torch.Size(n.shape).numel())
+                                      for n in self.model.state_needs)
+            pages = pool_pages_from_memory(groups, self.dtype, self.page_size, free - state_bytes, total,
                                            args.mem_fraction_static or 0.85)
             if pages < 1:
                 raise RuntimeError("no memory left for the KV cache; raise --mem-fraction-static or give "
