@@ -8,6 +8,10 @@
 // result are float32.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
 namespace lily {
 
 struct Operand {
@@ -154,6 +158,67 @@ __global__ void normed_mean_kernel(const NormedMeanArgs a, int stash) {
     }
 }
 
+// The same for a few tokens (decode): a thread-block cluster of CL blocks shares one token, each block takes
+// width / CL columns (four a thread) and the blocks exchange their sums of squares through distributed shared
+// memory, so that 8 tokens keep 64 SMs busy instead of 8.  grid (CL, tokens), cluster (CL, 1, 1);
+// width % (4 * CL) == 0; block = width / (4 * CL) threads.
+template <int CL>
+__global__ void normed_mean_cluster_kernel(const NormedMeanArgs a) {
+    __shared__ float red[MEAN_MAX][33];
+    __shared__ float share[MEAN_MAX][CL];
+    cg::cluster_group cluster = cg::this_cluster();
+    pdl_enter_small();
+    const size_t base = (size_t)blockIdx.y * a.width;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;       // this thread's four columns
+    float4 v[MEAN_MAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int k = 0; k < MEAN_MAX; ++k) {
+        float ssq = 0.f;
+        if (k < a.count) {
+            v[k] = a.in[k].four(base + i);
+            ssq = v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+        ssq = warp_sum(ssq);
+        if (lane == 0) red[k][warp] = ssq;
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int k = 0; k < MEAN_MAX; ++k) {
+            const float t = warp_sum(lane < nwarp ? red[k][lane] : 0.f);
+            if (lane == 0) red[k][32] = t;
+        }
+    }
+    __syncthreads();
+    // each block tells every block of the cluster its sums; after the one barrier nobody touches another block's
+    // shared memory again
+    if (threadIdx.x < CL) {
+#pragma unroll
+        for (int k = 0; k < MEAN_MAX; ++k) cluster.map_shared_rank(&share[k][0], threadIdx.x)[blockIdx.x] = red[k][32];
+    }
+    cluster.sync();
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < MEAN_MAX; ++k) {
+        if (k < a.count) {
+            float total = 0.f;
+#pragma unroll
+            for (int r = 0; r < CL; ++r) total += share[k][r];       // same order in every block
+            const float inv = rsqrtf(total / (float)a.width + a.eps);
+            const float4 g = *reinterpret_cast<const float4*>(a.gain[k] + i);
+            o.x += (v[k].x * inv) * g.x; o.y += (v[k].y * inv) * g.y;
+            o.z += (v[k].z * inv) * g.z; o.w += (v[k].w * inv) * g.w;
+        }
+    }
+    o.x *= a.scale; o.y *= a.scale; o.z *= a.scale; o.w *= a.scale;
+    if (a.add.p) {
+        const float4 f = a.add.four(base + i);
+        o.x += f.x; o.y += f.y; o.z += f.z; o.w += f.w;
+    }
+    *reinterpret_cast<float4*>(a.out + base + i) = o;
+}
+
 }  // namespace lily
 
 using namespace lily;
@@ -194,6 +259,25 @@ LILY_API int lily_normed_mean(const void* const* ins, const int* dtypes, const i
     a.out = out; a.width = width; a.eps = eps; a.scale = scale;
     bool vec = width % 4 == 0 && a.add.vector_ok() && ((uintptr_t)out & 15) == 0;
     for (int k = 0; k < count; ++k) vec = vec && a.in[k].vector_ok() && ((uintptr_t)gains[k] & 15) == 0;
+    constexpr int CL = 8;
+    if (vec && tokens <= 64 && width % (4 * CL) == 0 && width / (4 * CL) >= 32 && width / (4 * CL) <= 1024) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(CL, tokens);
+        cfg.blockDim = dim3(width / (4 * CL));
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = CL;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        cudaLaunchKernelEx(&cfg, normed_mean_cluster_kernel<CL>, a);
+        LILY_CHECK_LAUNCH("normed_mean");
+        return 0;
+    }
     // a few tokens: the block as wide as the row allows (few blocks are in flight, each should be short)
     int threads = width >= 2048 ? 512 : 256;
     if (tokens <= 64 && vec) threads = width / 4 >= 1024 ? 1024 : (width / 4 >= 512 ? 512 : threads);

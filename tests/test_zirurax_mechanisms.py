@@ -181,15 +181,21 @@ def test_gate_then_grouped_norm(device):
 def test_normed_mean_gate_and_gelu(device):
     ops = ops_for(device)
     g = torch.Generator().manual_seed(4)
+    # odd widths, and wide rows of a few tokens (which a cluster of blocks shares on the GPU) and of many
+    for n, width in ((19, 72), (5, 1024), (70, 1024), (3, 4096)):
+        a, b, f = (torch.randn(n, width, generator=g) * s for s in (5.0, 0.1, 1.0))
+        ga, gb = 1 + 0.2 * torch.randn(width, generator=g), 1 + 0.2 * torch.randn(width, generator=g)
+        want = 0.5 * (pz.rms(a, 1e-6) * ga + pz.rms(b, 1e-6) * gb) + f
+        parts = torch.stack([0.25 * a, 0.75 * a]).contiguous()                 # one input arrives as two partial sums
+        got = ops.normed_mean([parts.to(device), b.to(device)], [ga.to(device), gb.to(device)], 1e-6, add=f.to(device))
+        assert got.shape == (1, n, width) and float((got[0].cpu() - want).abs().max()) < 2e-5, (n, width)
+        alone = ops.normed_mean([b.to(device)], [gb.to(device)], 1e-6)
+        assert float((alone[0].cpu() - pz.rms(b, 1e-6) * gb).abs().max()) < 2e-5, (n, width)
+        half = ops.normed_mean([a.bfloat16().to(device), b.bfloat16().to(device)], [ga.to(device), gb.to(device)], 1e-6)
+        ref = 0.5 * (pz.rms(a.bfloat16().float(), 1e-6) * ga + pz.rms(b.bfloat16().float(), 1e-6) * gb)
+        assert float((half[0].cpu() - ref).abs().max()) < 2e-5, (n, width)
     n, width = 19, 72
-    a, b, f = (torch.randn(n, width, generator=g) * s for s in (5.0, 0.1, 1.0))
-    ga, gb = 1 + 0.2 * torch.randn(width, generator=g), 1 + 0.2 * torch.randn(width, generator=g)
-    want = 0.5 * (pz.rms(a, 1e-6) * ga + pz.rms(b, 1e-6) * gb) + f
-    parts = torch.stack([0.25 * a, 0.75 * a]).contiguous()                     # one input arrives as two partial sums
-    got = ops.normed_mean([parts.to(device), b.to(device)], [ga.to(device), gb.to(device)], 1e-6, add=f.to(device))
-    assert got.shape == (1, n, width) and float((got[0].cpu() - want).abs().max()) < 1e-5
-    alone = ops.normed_mean([b.to(device)], [gb.to(device)], 1e-6)
-    assert float((alone[0].cpu() - pz.rms(b, 1e-6) * gb).abs().max()) < 1e-5
+    a, b = torch.randn(n, width, generator=g) * 5.0, torch.randn(n, width, generator=g) * 0.1
 
     out = a.clone().to(device)
     ops.sigmoid_gate(out, b.to(device))
