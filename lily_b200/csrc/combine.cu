@@ -85,56 +85,35 @@ __global__ void sigmoid_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, cons
 
 // One block a token.  VEC 4: four columns a thread and turn (the width a multiple of four, everything 16-byte aligned).
 template <int VEC>
-__global__ void normed_mean_kernel(const NormedMeanArgs a, int stash) {
-    extern __shared__ __align__(16) float kept[];      // [count][width] when `stash`: every input is read once
-    __shared__ float red[MEAN_MAX][33];
+__global__ void normed_mean_kernel(const NormedMeanArgs a) {
+    __shared__ float red[33];
     pdl_enter_small();
     const size_t base = (size_t)blockIdx.x * a.width;
-    // one sweep over the row reads every input (kept in shared memory when `stash`) and sums their squares side by side
-    float ssq[MEAN_MAX];
-#pragma unroll
-    for (int k = 0; k < MEAN_MAX; ++k) ssq[k] = 0.f;
-    for (int i = threadIdx.x * VEC; i < a.width; i += blockDim.x * VEC) {
-#pragma unroll
-        for (int k = 0; k < MEAN_MAX; ++k) {
-            if (k < a.count) {
-                if (VEC == 4) {
-                    const float4 v = a.in[k].four(base + i);
-                    if (stash) *reinterpret_cast<float4*>(kept + (size_t)k * a.width + i) = v;
-                    ssq[k] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                } else {
-                    const float v = a.in[k](base + i);
-                    if (stash) kept[(size_t)k * a.width + i] = v;
-                    ssq[k] = fmaf(v, v, ssq[k]);
-                }
-            }
-        }
-    }
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
-#pragma unroll
-    for (int k = 0; k < MEAN_MAX; ++k) {
-        const float t = warp_sum(ssq[k]);
-        if (lane == 0) red[k][warp] = t;
-    }
-    __syncthreads();
-    if (warp == 0) {
-#pragma unroll
-        for (int k = 0; k < MEAN_MAX; ++k) {
-            const float t = warp_sum(lane < nwarp ? red[k][lane] : 0.f);
-            if (lane == 0) red[k][32] = t;
-        }
-    }
-    __syncthreads();
     float inv[MEAN_MAX];
 #pragma unroll
-    for (int k = 0; k < MEAN_MAX; ++k) inv[k] = rsqrtf(red[k][32] / (float)a.width + a.eps);
+    for (int k = 0; k < MEAN_MAX; ++k) {
+        inv[k] = 0.f;
+        if (k < a.count) {
+            float ssq = 0.f;
+            for (int i = threadIdx.x * VEC; i < a.width; i += blockDim.x * VEC) {
+                if (VEC == 4) {
+                    const float4 v = a.in[k].four(base + i);
+                    ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                } else {
+                    const float v = a.in[k](base + i);
+                    ssq = fmaf(v, v, ssq);
+                }
+            }
+            inv[k] = rsqrtf(block_sum(ssq, red) / (float)a.width + a.eps);
+        }
+    }
     for (int i = threadIdx.x * VEC; i < a.width; i += blockDim.x * VEC) {
         if (VEC == 4) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int k = 0; k < MEAN_MAX; ++k) {
                 if (k < a.count) {
-                    const float4 v = stash ? *reinterpret_cast<const float4*>(kept + (size_t)k * a.width + i) : a.in[k].four(base + i);
+                    const float4 v = a.in[k].four(base + i);
                     const float4 g = *reinterpret_cast<const float4*>(a.gain[k] + i);
                     o.x += (v.x * inv[k]) * g.x; o.y += (v.y * inv[k]) * g.y;
                     o.z += (v.z * inv[k]) * g.z; o.w += (v.w * inv[k]) * g.w;
@@ -150,7 +129,7 @@ __global__ void normed_mean_kernel(const NormedMeanArgs a, int stash) {
             float o = 0.f;
 #pragma unroll
             for (int k = 0; k < MEAN_MAX; ++k)
-                if (k < a.count) o += ((stash ? kept[(size_t)k * a.width + i] : a.in[k](base + i)) * inv[k]) * a.gain[k][i];
+                if (k < a.count) o += (a.in[k](base + i) * inv[k]) * a.gain[k][i];
             o *= a.scale;
             if (a.add.p) o += a.add(base + i);
             a.out[base + i] = o;
@@ -278,13 +257,9 @@ LILY_API int lily_normed_mean(const void* const* ins, const int* dtypes, const i
         LILY_CHECK_LAUNCH("normed_mean");
         return 0;
     }
-    // a few tokens: the block as wide as the row allows (few blocks are in flight, each should be short)
-    int threads = width >= 2048 ? 512 : 256;
-    if (tokens <= 64 && vec) threads = width / 4 >= 1024 ? 1024 : (width / 4 >= 512 ? 512 : threads);
-    const int stash = (size_t)count * width * sizeof(float) <= 40 * 1024;
-    const size_t smem = stash ? (size_t)count * width * sizeof(float) : 0;
-    if (vec) launch_pdl(normed_mean_kernel<4>, dim3(tokens), dim3(threads), smem, stream, a, stash);
-    else launch_pdl(normed_mean_kernel<1>, dim3(tokens), dim3(threads), smem, stream, a, stash);
+    const int threads = width >= 2048 ? 512 : 256;
+    if (vec) launch_pdl(normed_mean_kernel<4>, dim3(tokens), dim3(threads), 0, stream, a);
+    else launch_pdl(normed_mean_kernel<1>, dim3(tokens), dim3(threads), 0, stream, a);
     LILY_CHECK_LAUNCH("normed_mean");
     return 0;
 }

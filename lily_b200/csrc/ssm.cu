@@ -16,6 +16,9 @@
 namespace lily {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+// SiLU where the result is rounded to bfloat16 anyway: the fast exponential and quotient (float32 keeps the exact ones)
+template <typename T> __device__ __forceinline__ float silu_for(float v) { return silu_f(v); }
+template <> __device__ __forceinline__ float silu_for<__nv_bfloat16>(float v) { return __fdividef(v, 1.f + __expf(-v)); }
 
 __device__ __forceinline__ void copy16_async(void* smem_dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src));
@@ -64,10 +67,11 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
     for (int j = 0; j < TAPS; ++j) wt[j] = w[(size_t)c * TAPS + j];
     const float b = bias ? bias[c] : 0.f;
     T* dst = out + (size_t)(tok0 + start) * channels + c;
+    const T* from = src + (size_t)start * in_stride;
     for (int t = 0; t < n; t += 4) {                 // four tokens' inputs asked for before the first is used
         float xs[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) xs[u] = t + u < n ? to_float(src[(size_t)(start + t + u) * in_stride]) : 0.f;
+        for (int u = 0; u < 4; ++u) xs[u] = t + u < n ? to_float(from[(size_t)u * in_stride]) : 0.f;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             if (t + u < n) {
@@ -79,9 +83,11 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
 #pragma unroll
                 for (int j = 0; j + 1 < K1; ++j) win[j] = win[j + 1];
                 if (K1 > 0) win[K1 - 1] = x;
-                dst[(size_t)(t + u) * channels] = from_float<T>(silu_f(acc));
+                dst[(size_t)u * channels] = from_float<T>(silu_for<T>(acc));
             }
         }
+        from += (size_t)4 * in_stride;
+        dst += (size_t)4 * channels;
     }
     if (start == 0 && len <= chunk_len) {
 #pragma unroll
@@ -350,11 +356,29 @@ __global__ void ssd_combine_kernel(float* __restrict__ state, size_t state_strid
 
 // grid (tokens, groups), block 256: v = y * silu(z) over one group of `gsize` columns, normalised by the
 // group's own root mean square, times the gain.
+__device__ __forceinline__ float4 quad_of(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 quad_of(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void put_quad(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void put_quad(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// `quads`: four columns a thread and turn (sizes and offsets multiples of four, aligned bases; the launcher checks).
+// The gated values of the group are kept in shared memory (`stash`), so every input is read once.
 template <typename T>
 __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ z, int z_stride,
                                            const float* __restrict__ gain, T* __restrict__ out, int inner,
-                                           int gsize, float eps, int stash) {
-    extern __shared__ float gated[];          // [gsize] when `stash`: the gated values, formed once
+                                           int gsize, float eps, int stash, int quads) {
+    extern __shared__ __align__(16) float gated[];          // [gsize] when `stash`
     __shared__ float red[33];
     pdl_enter_small();
     const size_t t = blockIdx.x;
@@ -362,42 +386,39 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     const float* yr = y + t * inner + c0;
     const T* zr = z + t * z_stride + c0;
     float ssq = 0.f;
-    // two columns a thread and turn where the group and the rows allow it (even sizes: 8-byte and 4-byte accesses)
-    const bool pairs = (gsize & 1) == 0 && (inner & 1) == 0 && (z_stride & 1) == 0 && (c0 & 1) == 0;
-    if (pairs) {
-        for (int i = 2 * threadIdx.x; i < gsize; i += 2 * blockDim.x) {
-            const float2 yv = *reinterpret_cast<const float2*>(yr + i);
-            const float v0 = yv.x * silu_f(to_float(zr[i])), v1 = yv.y * silu_f(to_float(zr[i + 1]));
-            if (stash) *reinterpret_cast<float2*>(gated + i) = make_float2(v0, v1);
-            ssq += v0 * v0 + v1 * v1;
+    if (quads) {
+        for (int i = 4 * threadIdx.x; i < gsize; i += 4 * blockDim.x) {
+            const float4 yv = quad_of(yr + i), zv = quad_of(zr + i);
+            const float4 v = make_float4(yv.x * silu_for<T>(zv.x), yv.y * silu_for<T>(zv.y), yv.z * silu_for<T>(zv.z),
+                                         yv.w * silu_for<T>(zv.w));
+            if (stash) *reinterpret_cast<float4*>(gated + i) = v;
+            ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
     } else {
         for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
-            const float v = yr[i] * silu_f(to_float(zr[i]));
+            const float v = yr[i] * silu_for<T>(to_float(zr[i]));
             if (stash) gated[i] = v;
             ssq = fmaf(v, v, ssq);
         }
     }
     const float inv = rsqrtf(block_sum(ssq, red) / (float)gsize + eps);      // (its barriers also publish `gated`)
     T* dst = out + t * inner + c0;
-    if (pairs) {
-        for (int i = 2 * threadIdx.x; i < gsize; i += 2 * blockDim.x) {
-            float v0, v1;
+    if (quads) {
+        for (int i = 4 * threadIdx.x; i < gsize; i += 4 * blockDim.x) {
+            float4 v;
             if (stash) {
-                const float2 v = *reinterpret_cast<const float2*>(gated + i);
-                v0 = v.x; v1 = v.y;
+                v = *reinterpret_cast<const float4*>(gated + i);
             } else {
-                const float2 yv = *reinterpret_cast<const float2*>(yr + i);
-                v0 = yv.x * silu_f(to_float(zr[i])); v1 = yv.y * silu_f(to_float(zr[i + 1]));
+                const float4 yv = quad_of(yr + i), zv = quad_of(zr + i);
+                v = make_float4(yv.x * silu_for<T>(zv.x), yv.y * silu_for<T>(zv.y), yv.z * silu_for<T>(zv.z), yv.w * silu_for<T>(zv.w));
             }
-            const float2 gv = *reinterpret_cast<const float2*>(gain + c0 + i);
-            dst[i] = from_float<T>((v0 * inv) * gv.x);
-            dst[i + 1] = from_float<T>((v1 * inv) * gv.y);
+            const float4 gv = quad_of(gain + c0 + i);
+            put_quad(dst + i, make_float4((v.x * inv) * gv.x, (v.y * inv) * gv.y, (v.z * inv) * gv.z, (v.w * inv) * gv.w));
         }
         return;
     }
     for (int i = threadIdx.x; i < gsize; i += blockDim.x) {
-        const float v = stash ? gated[i] : yr[i] * silu_f(to_float(zr[i]));
+        const float v = stash ? gated[i] : yr[i] * silu_for<T>(to_float(zr[i]));
         dst[i] = from_float<T>((v * inv) * gain[c0 + i]);
     }
 }
@@ -520,12 +541,15 @@ LILY_API int lily_gated_group_rmsnorm(const float* y, const void* z, int z_strid
     const int gsize = inner / groups;
     const int stash = gsize <= 10240;              // 40 KB of shared memory hold the group's gated values
     const size_t smem = stash ? (size_t)gsize * sizeof(float) : 0;
+    const size_t item = dtype == kBF16 ? 2 : 4;
+    const int quads = gsize % 4 == 0 && inner % 4 == 0 && z_stride % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)gain % 16 == 0 &&
+                      (uintptr_t)z % (4 * item) == 0 && (uintptr_t)out % (4 * item) == 0;
     if (dtype == kBF16)
         launch_pdl(gated_group_rmsnorm_kernel<__nv_bfloat16>, grid, block, smem, stream, y, (const __nv_bfloat16*)z, z_stride,
-                   gain, (__nv_bfloat16*)out, inner, gsize, eps, stash);
+                   gain, (__nv_bfloat16*)out, inner, gsize, eps, stash, quads);
     else
         launch_pdl(gated_group_rmsnorm_kernel<float>, grid, block, smem, stream, y, (const float*)z, z_stride, gain,
-                   (float*)out, inner, gsize, eps, stash);
+                   (float*)out, inner, gsize, eps, stash, quads);
     LILY_CHECK_LAUNCH("gated_group_rmsnorm");
     return 0;
 }

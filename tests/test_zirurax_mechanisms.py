@@ -167,14 +167,19 @@ def test_scan_carries_its_state(device, heads, pd, n_state, groups):
 def test_gate_then_grouped_norm(device):
     ops = ops_for(device)
     g = torch.Generator().manual_seed(3)
-    for inner, groups in ((48, 4), (90, 1), (256, 2)):
+    for inner, groups, extra in ((48, 4, 11), (90, 1, 11), (256, 2, 11), (256, 2, 12), (2048, 2, 128), (40, 5, 4)):
         y = torch.randn(21, inner, generator=g) * 3
-        proj = torch.randn(21, inner + 11, generator=g)
+        proj = torch.randn(21, inner + extra, generator=g)       # rows of odd and of even length (16-byte accesses)
         gain = 1 + 0.2 * torch.randn(inner, generator=g)
         z = proj[:, :inner]
         want = pz.grouped_rms(y * (z * torch.sigmoid(z)), groups, 1e-5) * gain
         got = ops.gated_group_rmsnorm(y.to(device), proj.to(device), gain.to(device), groups, 1e-5).float().cpu()
-        assert float((got - want).abs().max()) < 1e-5
+        assert float((got - want).abs().max()) < 1e-5, (inner, groups, extra)
+        if device != "cpu":
+            zb = proj.bfloat16().float()[:, :inner]
+            ref = pz.grouped_rms(y * (zb * torch.sigmoid(zb)), groups, 1e-5) * gain
+            got = ops.gated_group_rmsnorm(y.to(device), proj.bfloat16().to(device), gain.to(device), groups, 1e-5).float().cpu()
+            assert float((got - ref).abs().max()) < 0.02 * float(ref.abs().max()), (inner, groups, extra)
 
 
 @pytest.mark.parametrize("device", DEVICES)
