@@ -6,7 +6,8 @@ window of them) form a *group*.  A group owns a pool of pages, one device tensor
 values at 1; page 0 is never handed out) and one block table per live request.  A page of one
 head is a contiguous ``[page_size, head_dim]`` tile.  Where the values have a head size of their own the tensor is
 ``[layers, pages + 1, kv_heads * page_size * (head_dim + v_head_dim)]``: a page's keys ``[kv_heads, page_size, head_dim]``
-followed by its values ``[kv_heads, page_size, v_head_dim]`` (the first form is this one with equal sizes).
+followed by its values ``[kv_heads, page_size, v_head_dim]`` (the first form is this one with equal sizes); where the
+values are columns of the key rows themselves (``CacheNeed.values_in_keys``) a page is its keys alone.
 
 A request takes a slot when it is opened, grows page by page as its tokens arrive (all
 groups together, or not at all: ``OutOfPages``), gives pages of windowed groups back as the
@@ -45,7 +46,14 @@ class CacheGroup:
 def bytes_per_token(groups: Sequence[Tuple[CacheNeed, int]], dtype: torch.dtype) -> int:
     """Bytes of keys and values one token takes over all layers (model_runner.py:160-164)."""
     item = torch.empty((), dtype=dtype).element_size()
-    return sum(need.kv_heads * (need.head_dim + (need.v_head_dim or need.head_dim)) * layers * item for need, layers in groups)
+    return sum(need.kv_heads * (need.head_dim + value_columns(need)) * layers * item for need, layers in groups)
+
+
+def value_columns(need: CacheNeed) -> int:
+    """Columns a cached position takes for its values besides its keys (none when the values are read out of the key rows)."""
+    if need.values_in_keys:
+        return 0
+    return need.head_dim if need.v_head_dim is None else need.v_head_dim
 
 
 class KVCacheManager:
@@ -66,8 +74,9 @@ class KVCacheManager:
         for need, layers in groups:
             data = None
             if device is not None:
-                shape = (2, need.kv_heads, page_size, need.head_dim) if need.v_head_dim in (None, need.head_dim) else \
-                    (need.kv_heads * page_size * (need.head_dim + need.v_head_dim),)
+                same = need.v_head_dim in (None, need.head_dim) and not need.values_in_keys
+                shape = (2, need.kv_heads, page_size, need.head_dim) if same else \
+                    (need.kv_heads * page_size * (need.head_dim + value_columns(need)),)
                 data = torch.zeros((layers, num_pages + 1, *shape), dtype=dtype, device=device)
             self.groups.append(CacheGroup(need, layers, GroupTables(num_pages, page_size, need.window), data))
         self.states: List[Optional[torch.Tensor]] = []

@@ -1,7 +1,8 @@
 """One registry from an architecture's name to its typed configuration and model builder.
 
 An architecture is two functions: ``config_from_dict(config.json, generation_config.json)``
-returning its typed configuration, and ``build_spec(config)`` returning a ``ModelSpec``
+returning its typed configuration (which may offer ``sizes_from_tensors(shapes)`` for sizes that only the checkpoint's
+tensor shapes give), and ``build_spec(config)`` returning a ``ModelSpec``
 (a list of blocks made of registered parts, and the order in which they run).  The
 loader, cache manager, step function, scheduler, sampler and replay tool know nothing
 else about a model.

@@ -5,7 +5,8 @@
 // Cache layout of one layer: [pages, 2 (keys, values), kv_heads, page_size, head_dim]; a
 // request's block table gives the page of each run of page_size positions.  Values may have a head
 // size of their own (`dv`): a page is then its keys [kv_heads, page_size, d] followed by its values
-// [kv_heads, page_size, dv], and outputs have dv columns a head.
+// [kv_heads, page_size, dv], and outputs have dv columns a head.  Or the values are the first dv columns of the key
+// rows themselves (`v_in_k`, attention over a cached latent that serves as key and value): a page is then its keys alone.
 //
 //  * prefill: grid (query tiles, query heads).  A tile is up to 32 consecutive new tokens of one
 //    request; their keys are the request's cached prefix and the new tokens up to each query
@@ -37,8 +38,10 @@ attention_simt_kernel(const AttnArgs a) {
     const int d = a.d, dv = a.dv;
     float* Qs = smem;                          // [ROWS][d]
     float* Ks = Qs + ROWS * d;                 // [KEYS][d + 1]
-    float* Vs = Ks + KEYS * (d + 1);           // [KEYS][dv]
-    float* Ps = Vs + KEYS * dv;                // [WARPS][RPW][KEYS]
+    float* Vs = Ks + KEYS * (d + 1);           // [KEYS][dv] (none when the values are read out of the key rows)
+    float* Ps = Vs + (a.v_in_k ? 0 : KEYS * dv);   // [WARPS][RPW][KEYS]
+    const float* Vp = a.v_in_k ? Ks : Vs;
+    const int vrow = a.v_in_k ? d + 1 : dv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const T* q = (const T*)a.q;
     const T* kv = (const T*)a.kv;
@@ -107,7 +110,7 @@ attention_simt_kernel(const AttnArgs a) {
     }
 
     const int* table = a.block_table + (size_t)req * a.bt_stride;
-    const size_t khead = (size_t)a.page_size * d, vhead = (size_t)a.page_size * dv;     // one head's tiles in a page
+    const size_t khead = (size_t)a.page_size * d, vhead = a.v_in_k ? 0 : (size_t)a.page_size * dv;     // one head's tiles in a page
     const size_t page_stride = (size_t)a.nkv * (khead + vhead);
     const float cap = a.softcap, cap_in = cap > 0.f ? a.scale / cap : 0.f;
 
@@ -122,10 +125,12 @@ attention_simt_kernel(const AttnArgs a) {
                 const T* ksrc = base + (size_t)kvh * khead + (size_t)(kpos % a.page_size) * d;
                 const T* vsrc = base + (size_t)a.nkv * khead + (size_t)kvh * vhead + (size_t)(kpos % a.page_size) * dv;
                 for (int c = lane; c < d; c += 32) Ks[j * (d + 1) + c] = to_float(ksrc[c]);
-                for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = to_float(vsrc[c]);
+                if (!a.v_in_k)
+                    for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = to_float(vsrc[c]);
             } else {
                 for (int c = lane; c < d; c += 32) Ks[j * (d + 1) + c] = 0.f;
-                for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = 0.f;
+                if (!a.v_in_k)
+                    for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = 0.f;
             }
         }
         __syncthreads();
@@ -168,7 +173,7 @@ attention_simt_kernel(const AttnArgs a) {
 #pragma unroll
             for (int c = 0; c < DCH; ++c) {
                 const int col = lane + 32 * c;
-                v[c] = col < dv ? Vs[j * dv + col] : 0.f;
+                v[c] = col < dv ? Vp[j * vrow + col] : 0.f;
             }
 #pragma unroll
             for (int i = 0; i < RPW; ++i) {
@@ -291,12 +296,12 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     }
 }
 
-static size_t smem_bytes(int d, int dv) { return sizeof(float) * ((size_t)ROWS * d + KEYS * (d + 1) + KEYS * dv + ROWS * KEYS); }
+static size_t smem_bytes(int d, int dv, int v_in_k) { return sizeof(float) * ((size_t)ROWS * d + KEYS * (d + 1) + (v_in_k ? 0 : KEYS * dv) + ROWS * KEYS); }
 
 template <typename T, bool DECODE>
 static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
     const int dch = (a.dv + 31) / 32;              // output columns a lane owns
-    const size_t smem = smem_bytes(a.d, a.dv);
+    const size_t smem = smem_bytes(a.d, a.dv, a.v_in_k);
 #define CASE(N)                                                                                          \
     case N: {                                                                                            \
         auto kern = attention_simt_kernel<T, N, DECODE>;                                                 \
@@ -310,9 +315,9 @@ static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
         break;                                                                                           \
     }
     switch (dch) {
-        CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8)
+        CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8) CASE(9) CASE(10) CASE(11) CASE(12) CASE(13) CASE(14) CASE(15) CASE(16)
         default:
-            set_error("attention: value head size %d is beyond the 256 this kernel takes", a.dv);
+            set_error("attention: value head size %d is beyond the 512 this kernel takes", a.dv);
             return 1;
     }
 #undef CASE
@@ -321,8 +326,9 @@ static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
 
 static int check_common(const char* name, int nq, int nkv, int d, int page_size, int dv) {
     LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "%s: %d query heads do not group over %d kv heads", name, nq, nkv);
-    LILY_REQUIRE(d > 0 && d <= 256, "%s: head_dim %d is outside 1..256", name, d);
-    LILY_REQUIRE(dv >= 0 && dv <= 256, "%s: value head size %d is outside 1..256", name, dv);
+    // dv < 0: the values are the first -dv columns of the key rows
+    LILY_REQUIRE(d > 0 && d <= 640, "%s: head_dim %d is outside 1..640", name, d);
+    LILY_REQUIRE(dv >= -d && dv <= 512 && dv >= -512, "%s: value head size %d is outside 1..512 (or the key's)", name, dv < 0 ? -dv : dv);
     LILY_REQUIRE(page_size > 0, "%s: page_size %d", name, page_size);
     return 0;
 }
@@ -343,7 +349,7 @@ LILY_API int lily_attention_prefill_simt(const void* q, const void* kv, void* ou
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
     a.cu_seqlens = cu_seqlens; a.prefix_lens = prefix_lens; a.tile_req = tile_req; a.tile_start = tile_start;
     a.splits = 1; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
-    a.softcap = softcap; a.dv = dv > 0 ? dv : d;
+    a.softcap = softcap; a.dv = dv > 0 ? dv : (dv < 0 ? -dv : d); a.v_in_k = dv < 0;
     dim3 grid(tiles, nq);
     int rc = dtype == kBF16 ? launch<__nv_bfloat16, false>(a, grid, stream) : launch<float, false>(a, grid, stream);
     if (rc) return rc;
@@ -380,14 +386,14 @@ LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out
                                         float scale, int dtype, float softcap, int dv, cudaStream_t stream) {
     if (requests == 0) return 0;
     if (check_common("attention_decode", nq, nkv, d, page_size, dv)) return 1;
-    const int d_out = dv > 0 ? dv : d;
+    const int d_out = dv > 0 ? dv : (dv < 0 ? -dv : d);
     LILY_REQUIRE(splits >= 1 && splits <= 65535, "attention_decode: %d splits", splits);
     LILY_REQUIRE(splits == 1 || scratch != nullptr, "attention_decode: splits need scratch");
     const int group = nq / nkv, chunks = (group + ROWS - 1) / ROWS;
     AttnArgs a{};
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
     a.seq_lens = seq_lens; a.splits = splits; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size;
-    a.window = window; a.scale = scale; a.softcap = softcap; a.dv = d_out;
+    a.window = window; a.scale = scale; a.softcap = softcap; a.dv = d_out; a.v_in_k = dv < 0;
     a.part_o = scratch;
     a.part_ml = scratch ? scratch + (size_t)requests * nq * splits * d_out : nullptr;
     dim3 grid(requests, nkv * chunks, splits);

@@ -241,6 +241,43 @@ __global__ void add_rmsnorm_cluster_kernel(float* __restrict__ resid, const Summ
     store4(out + (size_t)m * hidden, i, make_float4((v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w));
 }
 
+
+// ---------------------------------------------------------------------------- add (several) + RMSNorm (two gains)
+
+// The general form for blocks with parallel sublayers: one block per row,
+//   v = resid (+ delta_a) (+ delta_b) (+ bias[column]);  resid = v  (when write_residual)
+//   out_a = v * rsqrt(mean(v^2) + eps) * gain_a;  out_b = the same with gain_b (when given)
+// The deltas may be partial sums; the bias is a float32 row vector added to every row of the stream.
+template <typename T, typename INA, typename INB>
+__global__ void add_rmsnorm_multi_kernel(float* __restrict__ resid, const Summed<INA> da, const Summed<INB> db,
+                                         const float* __restrict__ bias, const float* __restrict__ gain_a,
+                                         const float* __restrict__ gain_b, T* __restrict__ out_a, T* __restrict__ out_b,
+                                         int hidden, float eps, int write_residual) {
+    extern __shared__ __align__(16) float smem[];
+    pdl_enter_small();
+    float* red = smem;             // 33 floats
+    float* row = smem + 40;        // hidden floats
+    const size_t src = (size_t)blockIdx.x * hidden;
+    float ssq = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = resid[src + i];
+        float add = 0.f;
+        if (da) add = da(src + i);
+        if (db) add += db(src + i);
+        v += add;
+        if (bias) v += bias[i];
+        if (write_residual) resid[src + i] = v;
+        row[i] = v;
+        ssq = fmaf(v, v, ssq);
+    }
+    const float inv = rsqrtf(block_sum(ssq, red) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = row[i] * inv;
+        if (out_a) out_a[src + i] = from_float<T>(v * gain_a[i]);
+        if (out_b) out_b[src + i] = from_float<T>(v * gain_b[i]);
+    }
+}
+
 // ---------------------------------------------------------------------------- SiLU * mul
 
 __device__ __forceinline__ float silu_times(float g, float u) { return (g / (1.f + expf(-g))) * u; }
@@ -634,6 +671,44 @@ LILY_API int lily_add_rmsnorm(float* resid, const void* delta, const void* weigh
     }
 #undef GO
     LILY_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+}
+
+template <typename T, typename INA, typename INB>
+static void launch_add_rmsnorm_multi(float* resid, const void* da, int sa, size_t stra, const void* db, int sb, size_t strb,
+                                     const float* bias, const float* gain_a, const float* gain_b, void* out_a, void* out_b,
+                                     int rows, int hidden, float eps, int write_residual, cudaStream_t stream) {
+    const Summed<INA> a{(const INA*)da, sa, stra};
+    const Summed<INB> b{(const INB*)db, sb, strb};
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    launch_pdl(add_rmsnorm_multi_kernel<T, INA, INB>, dim3(rows), dim3(threads), (size_t)(40 + hidden) * sizeof(float), stream,
+               resid, a, b, bias, gain_a, gain_b, (T*)out_a, (T*)out_b, hidden, eps, write_residual);
+}
+
+// resid += delta_a + delta_b + bias (each optional), then one or two RMSNorms of the new rows with float32 gains.
+LILY_API int lily_add_rmsnorm_multi(float* resid, const void* delta_a, int a_dtype, int a_splits, size_t a_stride,
+                                    const void* delta_b, int b_dtype, int b_splits, size_t b_stride, const float* bias,
+                                    const float* gain_a, const float* gain_b, void* out_a, void* out_b, int rows, int hidden,
+                                    float eps, int write_residual, int act_dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    LILY_REQUIRE(hidden > 0 && hidden <= 11264, "add_rmsnorm_multi: hidden=%d (rows of up to 11264 numbers)", hidden);
+    LILY_REQUIRE((out_a == nullptr) == (gain_a == nullptr) && (out_b == nullptr) == (gain_b == nullptr), "add_rmsnorm_multi: an output needs its gain");
+    if (delta_a && check_summed("add_rmsnorm_multi", act_dtype, a_dtype, a_splits)) return 1;
+    if (delta_b && check_summed("add_rmsnorm_multi", act_dtype, b_dtype, b_splits)) return 1;
+    if (!delta_a) a_dtype = kF32;
+    if (!delta_b) b_dtype = kF32;
+#define GO(T, INA, INB) launch_add_rmsnorm_multi<T, INA, INB>(resid, delta_a, a_splits, a_stride, delta_b, b_splits, b_stride, bias, gain_a, gain_b, out_a, out_b, rows, hidden, eps, write_residual, stream)
+    if (act_dtype == kBF16) {
+        const bool ab = a_dtype == kBF16, bb = b_dtype == kBF16;
+        if (ab && bb) GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+        else if (ab) GO(__nv_bfloat16, __nv_bfloat16, float);
+        else if (bb) GO(__nv_bfloat16, float, __nv_bfloat16);
+        else GO(__nv_bfloat16, float, float);
+    } else {
+        GO(float, float, float);
+    }
+#undef GO
+    LILY_CHECK_LAUNCH("add_rmsnorm_multi");
     return 0;
 }
 

@@ -14,7 +14,11 @@ constexpr int RUN = 256;               // products per run (a multiple of BK)
 
 __global__ void __launch_bounds__(256)
 gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
-                 float* __restrict__ C, int M, int N, int K, int lda, int ldc) {
+                 float* __restrict__ C, int M, int N, int K, int lda, int ldc, size_t a_head, size_t w_head, size_t c_head) {
+    // blockIdx.z: one of several products of the same sizes (a product per head), their operands these strides apart
+    A += blockIdx.z * a_head;
+    W += blockIdx.z * w_head;
+    C += blockIdx.z * c_head;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -75,7 +79,20 @@ LILY_API int lily_gemm_fp32(const float* A, const float* W, const float* bias, f
     LILY_REQUIRE(K > 0 && lda >= K && ldc >= N, "gemm_fp32: bad sizes M=%d N=%d K=%d lda=%d ldc=%d", M, N, K, lda, ldc);
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     LILY_REQUIRE(grid.y <= 65535, "gemm_fp32: M=%d is too large for one launch", M);
-    gemm_fp32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldc);
+    gemm_fp32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldc, 0, 0, 0);
     LILY_CHECK_LAUNCH("gemm_fp32");
+    return 0;
+}
+
+// `heads` products of the same sizes in one launch: head h reads A + h * a_head (rows lda apart) and W + h * w_head
+// ([N, K]) and writes C + h * c_head (rows ldc apart).
+LILY_API int lily_gemm_fp32_heads(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldc, int heads,
+                                  size_t a_head, size_t w_head, size_t c_head, cudaStream_t stream) {
+    if (M == 0 || N == 0 || heads == 0) return 0;
+    LILY_REQUIRE(K > 0 && lda >= K && ldc >= N && heads <= 65535, "gemm_fp32_heads: bad sizes M=%d N=%d K=%d lda=%d ldc=%d heads=%d", M, N, K, lda, ldc, heads);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, heads);
+    LILY_REQUIRE(grid.y <= 65535, "gemm_fp32_heads: M=%d is too large for one launch", M);
+    gemm_fp32_kernel<<<grid, 256, 0, stream>>>(A, W, nullptr, C, M, N, K, lda, ldc, a_head, w_head, c_head);
+    LILY_CHECK_LAUNCH("gemm_fp32_heads");
     return 0;
 }

@@ -50,6 +50,20 @@ _SIGNATURES = {
                       _i, _vp, _vp, _i, _vp],
     "lily_ssd_combine": [_vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lily_gated_group_rmsnorm": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+    "lily_add_rmsnorm_multi": [_vp, _vp, _i, _i, _sz, _vp, _i, _i, _sz, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp],
+    "lily_gemm_fp32_heads": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _sz, _sz, _vp],
+    "lily_token_shift_mix": [_vp, _i, _i, _vp, _i, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _i, _vp],
+    "lily_wkv_decay": [_vp, _i, _i, _vp, _vp, _i, _vp, _vp],
+    "lily_wkv_scan": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "lily_group_rmsnorm_gate": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+    "lily_latent_prepare": [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp,
+                            _i, _i, _vp],
+    "lily_latent_query": [_vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp],
+    "lily_head_gate": [_vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],
+    "lily_moe_route": [_vp, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _i, _vp],
+    "lily_moe_align": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp],
+    "lily_moe_gemm": [_i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _f, _f, _i, _vp],
+    "lily_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_top_logprobs": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -90,6 +104,8 @@ def library():
         lib.lily_attention_decode_scratch_floats.argtypes = [_i, _i, _i, _i]
         lib.lily_attention_decode_scratch_floats.restype = _sz
         lib.lily_normed_mean_max.restype = _i
+        lib.lily_wkv_max_head_dim.restype = _i
+        lib.lily_moe_tile_rows.restype = _i
         _lib = lib
     return _lib
 
@@ -218,6 +234,40 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
           int(write_residual), _dt(out), _dt(weight), _dt(delta) if delta is not None else _dt(out), splits, stride,
           _stream())
     return out
+
+
+def add_rmsnorm_multi(resid: torch.Tensor, deltas: Sequence[torch.Tensor], gains: Sequence[torch.Tensor], eps: float,
+                      out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None,
+                      write_residual: bool = True) -> Tuple[torch.Tensor, ...]:
+    """``resid += sum(deltas) + bias`` (float32, in place), then one RMSNorm of the new rows per entry of ``gains``
+    (float32 vectors; none, one or two), all from the same root mean square.  ``deltas`` holds up to two tensors, each
+    [tokens, hidden] in the activation dtype or float32 partial sums; ``bias`` is a float32 vector [hidden] added to
+    every row.  Returns the normed activations, one tensor per gain."""
+    deltas = [d for d in deltas if d is not None]
+    if len(deltas) > 2 or len(gains) > 2:
+        raise KernelError("add_rmsnorm_multi takes up to two deltas and up to two gains")
+    _dev(resid, bias, *deltas, *gains)
+    if resid.dtype != torch.float32:
+        raise KernelError("the residual stream is float32")
+    rows, hidden = resid.shape
+    for g in gains:
+        if g.dtype != torch.float32 or g.numel() != hidden:
+            raise KernelError("add_rmsnorm_multi: gains are float32 vectors of the row's length")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != hidden):
+        raise KernelError("add_rmsnorm_multi: the bias is a float32 vector of the row's length")
+    outs = [torch.empty((rows, hidden), dtype=out_dtype, device=resid.device) for _ in gains]
+    desc = []
+    for d in deltas:
+        splits, stride = _summed(d, rows, hidden, "add_rmsnorm_multi delta")
+        if d.dtype not in (out_dtype, torch.float32):
+            raise KernelError(f"delta {d.dtype} does not match out {out_dtype}")
+        desc += [_p(d), _dt(d), splits, stride]
+    desc += [None, _F32, 1, 0] * (2 - len(deltas))
+    act = _BF16 if out_dtype == torch.bfloat16 else _F32
+    _call("lily_add_rmsnorm_multi", _p(resid), *desc, _p(bias), _p(gains[0]) if gains else None,
+          _p(gains[1]) if len(gains) > 1 else None, _p(outs[0]) if gains else None, _p(outs[1]) if len(gains) > 1 else None,
+          rows, hidden, float(eps), int(write_residual), act, _stream())
+    return tuple(outs)
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
@@ -480,11 +530,11 @@ def uses_tcgen05_attention(dtype: torch.dtype, d: int, page_size: int, new_token
 
 
 def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size: int = 0, new_tokens: int = 0,
-                      softcap: Optional[float] = None, dv: Optional[int] = None) -> int:
+                      softcap: Optional[float] = None, dv: Optional[int] = None, values_in_keys: bool = False) -> int:
     """New tokens per tile of the prefill kernel that will take this precision, head size (``dv`` for the values
     where it differs), page size, number of new tokens and kind of scores."""
     lib = library()
-    same = dv is None or dv == d
+    same = (dv is None or dv == d) and not values_in_keys
     if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens):
         return int(lib.lily_attention_prefill_tc_rows())
     return int(lib.lily_attention_prefill_mma_rows() if same and uses_tensor_cores(dtype, d) else lib.lily_attention_prefill_simt_rows())
@@ -499,10 +549,11 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
                       prefix_lens: torch.Tensor, tile_req: torch.Tensor, tile_start: torch.Tensor, out: torch.Tensor,
                       nq: int, nkv: int, d: int, page_size: int, scale: float, window: Optional[int] = None,
                       tile_rows: Optional[int] = None, heads_per_block: int = 0, softcap: Optional[float] = None,
-                      dv: Optional[int] = None) -> None:
+                      dv: Optional[int] = None, values_in_keys: bool = False) -> None:
     """Causal attention of each request's new tokens over its cached prefix and themselves.  ``softcap``: scores
     become softcap * tanh(score * scale / softcap) before the softmax; ``dv``: the
     value head size where it differs from d (CUDA-core kernels; ``out`` is then [tokens, nq * dv]).
+    ``values_in_keys``: the values are the first ``dv`` columns of the key rows and a page holds keys only (CUDA-core kernels).
     ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)
     in steps of ``tile_rows`` (default: ``prefill_tile_rows(q.dtype, d)``), which also names the
     kernel: the tcgen05 kernel takes tiles of its own size, the others theirs.  ``heads_per_block``
@@ -516,7 +567,7 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
     lib = library()
     dv = int(dv or d)
     cap = float(softcap or 0.0)
-    tensor_cores = dv == d and uses_tensor_cores(q.dtype, d)
+    tensor_cores = dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d)
     base_rows = int(lib.lily_attention_prefill_mma_rows() if tensor_cores else lib.lily_attention_prefill_simt_rows())
     if tile_rows is not None and tile_rows != base_rows:
         if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16 and dv == d
@@ -529,7 +580,7 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
     elif tensor_cores:
         _call("lily_attention_prefill_mma", *common, cap, _stream())
     else:
-        _call("lily_attention_prefill_simt", *common, _dt(q), cap, dv, _stream())
+        _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, _stream())
 
 
 def decode_clusters(d: int, splits: int, group: int) -> int:
@@ -545,7 +596,7 @@ def decode_scratch_floats(requests: int, nq: int, d: int, splits: int) -> int:
 def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
                      out: torch.Tensor, scratch: Optional[torch.Tensor], splits: int, nq: int, nkv: int, d: int,
                      page_size: int, scale: float, window: Optional[int] = None, stages: int = 0,
-                     softcap: Optional[float] = None, dv: Optional[int] = None) -> None:
+                     softcap: Optional[float] = None, dv: Optional[int] = None, values_in_keys: bool = False) -> None:
     """One query token per request (rows of ``q`` [requests, nq * d]) over ``seq_lens`` cached
     positions, keys cut into ``splits`` ranges merged through ``scratch`` (float32).  ``stages`` (tensor-core
     kernel only): the key/value tiles a block holds, 0 for the default (``DecodePlan.stages``)."""
@@ -561,14 +612,14 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
               _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0),
               float(scale))
-    if dv == d and uses_tensor_cores(q.dtype, d):
+    if dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d):
         _call("lily_attention_decode_mma", *common, int(stages), cap, _stream())   # merges the splits itself (cluster, or combine behind)
         if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
             launches["count"] += 1                                   # the combine kernel, launched inside
     else:
         if stages:
             raise KernelError(f"attention_decode: {stages} stages are the tensor-core kernel's; {q.dtype}, head size {d} runs on CUDA cores")
-        _call("lily_attention_decode_simt", *common, _dt(q), cap, dv, _stream())
+        _call("lily_attention_decode_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, _stream())
         if splits > 1:
             launches["count"] += 1          # the combine kernel, launched inside
 
@@ -648,7 +699,7 @@ def whole_rows_pay(pairs: int, sm_count: int = 148) -> bool:
 
 
 def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, d: int, max_seq_len: int,
-                          even: bool = False, dv: Optional[int] = None) -> DecodePlan:
+                          even: bool = False, dv: Optional[int] = None, values_in_keys: bool = False) -> DecodePlan:
     """The plan for ``requests`` rows that bring one token each, none longer than ``max_seq_len`` positions.
     A step in which every request brings one token may hand the qkv product straight to the attention kernel
     (``fused``): every block then finishes its own queries, which costs less than a kernel of its own while all
@@ -662,7 +713,7 @@ def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, 
         return DecodePlan(1, False, 0, "single")
     group = nq // nkv
     dv = int(dv or d)
-    tensor_cores = dv == d and uses_tensor_cores(dtype, d)      # values of another head size run on CUDA cores
+    tensor_cores = dv == d and not values_in_keys and uses_tensor_cores(dtype, d)      # values of another head size run on CUDA cores
     row_blocks = -(-group // 16)                 # the tensor-core kernel takes 16 query heads of a kv head a block
     pairs = requests * nkv * row_blocks
     if even and tensor_cores and d <= 128 and _WHOLE_ROWS and whole_rows_pay(pairs, sm_count()):
@@ -916,6 +967,230 @@ def gated_group_rmsnorm(y: torch.Tensor, proj: torch.Tensor, gain: torch.Tensor,
     out = torch.empty((n, inner), dtype=proj.dtype, device=y.device)
     _call("lily_gated_group_rmsnorm", _p(y), _p(proj), proj.shape[1], _p(gain), _p(out), n, inner, int(groups), float(eps),
           _dt(proj), _stream())
+    return out
+
+
+
+# ------------------------------------------------------------------------------ per-head products
+
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """One product per head: ``x`` [tokens, heads, k] (a view whose last axis is contiguous; the heads may be columns
+    of a wider row), ``weight`` [heads, n, k]; returns [heads, tokens, n].  float32: this package's FFMA kernel, a
+    head a grid plane; bfloat16: the library's batched product with float32 accumulation (``out_dtype=float32``
+    keeps the accumulator's precision)."""
+    _dev(weight)
+    tokens, heads, k = x.shape
+    if not x.is_cuda or x.stride(2) != 1 or weight.shape[0] != heads or weight.shape[2] != k or weight.dtype != x.dtype:
+        raise KernelError(f"head_linear: x {tuple(x.shape)} {x.dtype} strides {x.stride()} against weight {tuple(weight.shape)} {weight.dtype}")
+    n = weight.shape[1]
+    if x.dtype == torch.float32:
+        out = torch.empty((heads, tokens, n), dtype=torch.float32, device=x.device)
+        _call("lily_gemm_fp32_heads", _p(x), _p(weight), _p(out), tokens, n, k, x.stride(0), n, heads, x.stride(1), n * k,
+              tokens * n, _stream())
+        return out
+    if out_dtype == torch.float32:
+        return torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out_dtype=torch.float32)
+    return torch.bmm(x.transpose(0, 1), weight.transpose(1, 2))
+
+
+# ------------------------------------------------------------------------------ linear attention with a data-dependent decay
+
+def token_shift_mix(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, state_off: int, cu_seqlens: torch.Tensor,
+                    token_req: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """``out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]`` for each row s of ``mu`` (float32 [streams, width]); ahead of a
+    request's first new token stands the input its slot carries (``state`` float32 [slots, row], from column
+    ``state_off`` on; zeros for a new request), and the slot then takes the request's last new input.
+    Returns [streams, tokens, width] in ``h``'s dtype."""
+    _dev(h, mu, state, cu_seqlens, token_req, slots)
+    tokens, width = h.shape
+    if mu.dtype != torch.float32 or mu.shape[-1] != width or state.dtype != torch.float32:
+        raise KernelError("token_shift_mix: mu and the state are float32, mu [streams, width]")
+    if state_off + width > state.shape[1]:
+        raise KernelError("token_shift_mix: the carried input does not fit the state row")
+    streams = mu.shape[0]
+    out = torch.empty((streams, tokens, width), dtype=h.dtype, device=h.device)
+    _call("lily_token_shift_mix", _p(h), tokens, width, _p(mu), streams, _p(state), state.stride(0), state_off,
+          _i32(cu_seqlens, "cu_seqlens"), _i32(token_req, "token_req"), _i32(slots, "slots"), _p(out), _dt(h), _stream())
+    return out
+
+
+def wkv_decay(a: torch.Tensor, w2t: torch.Tensor, w0: torch.Tensor) -> torch.Tensor:
+    """The logarithm of the decay, ``-exp(w0 + tanh(a) . w2t)``: ``a`` [tokens, rank], ``w2t`` [rank, columns],
+    ``w0`` [columns], all float32; returns float32 [tokens, columns]."""
+    _dev(a, w2t, w0)
+    if a.dtype != torch.float32 or w2t.dtype != torch.float32 or w0.dtype != torch.float32:
+        raise KernelError("wkv_decay works in float32")
+    tokens, rank = a.shape
+    cols = w2t.shape[1]
+    if w2t.shape[0] != rank or w0.numel() != cols:
+        raise KernelError(f"wkv_decay: a {tuple(a.shape)}, w2t {tuple(w2t.shape)}, w0 {tuple(w0.shape)}")
+    out = torch.empty((tokens, cols), dtype=torch.float32, device=a.device)
+    _call("lily_wkv_decay", _p(a), tokens, rank, _p(w2t), _p(w0), cols, _p(out), _stream())
+    return out
+
+
+def wkv_max_head_dim() -> int:
+    return int(library().lily_wkv_max_head_dim())
+
+
+def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch.Tensor, u: torch.Tensor,
+             state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, requests: int, heads: int,
+             d: int) -> torch.Tensor:
+    """The recurrence, a request's new tokens one after another from and to the head matrices in its slot (the first
+    ``heads * d * d`` numbers of the row, [head, key row, value column]):
+    ``o_t = (S + diag(u) k_t v_t^T)^T r_t``, then ``S <- diag(exp(log_decay_t)) S + k_t v_t^T``.
+    ``r``, ``k``, ``v`` [tokens, heads * d] in the activation dtype (rows of equal stride), ``log_decay`` float32
+    [tokens, heads * d], ``u`` float32 [heads, d].  Returns float32 [tokens, heads * d]."""
+    _dev(log_decay, u, state, cu_seqlens, slots)
+    tokens = r.shape[0]
+    stride = r.stride(0)
+    for t in (r, k, v):
+        if not t.is_cuda or t.dtype != r.dtype or t.stride(1) != 1 or t.stride(0) != stride or t.shape != (tokens, heads * d):
+            raise KernelError("wkv_scan: r, k and v are [tokens, heads * d] of one dtype and row stride")
+    if log_decay.dtype != torch.float32 or u.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("wkv_scan: decay, bonus and state are float32")
+    if state.shape[1] < heads * d * d:
+        raise KernelError("wkv_scan: the state row is too short for the head matrices")
+    y = torch.empty((tokens, heads * d), dtype=torch.float32, device=r.device)
+    _call("lily_wkv_scan", _p(r), _p(k), _p(v), stride, _p(log_decay), _p(u), _p(state), state.stride(0), _p(y),
+          _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), requests, heads, d, _dt(r), _stream())
+    return y
+
+
+def group_rmsnorm_gate(y: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
+    """``y / rms(y over the column's group) * gain * silu(gate)``: ``y`` float32 [tokens, inner], ``gate`` [tokens, inner]
+    in the activation dtype (its rows may be strided), ``gain`` float32 [inner]; returns the gate's dtype."""
+    _dev(y, gain)
+    tokens, inner = y.shape
+    if y.dtype != torch.float32 or gain.dtype != torch.float32 or gate.shape != y.shape or gate.stride(1) != 1:
+        raise KernelError("group_rmsnorm_gate: y and the gain are float32, the gate has y's shape")
+    out = torch.empty((tokens, inner), dtype=gate.dtype, device=y.device)
+    _call("lily_group_rmsnorm_gate", _p(y), _p(gate), gate.stride(0), _p(gain), _p(out), tokens, inner, groups, float(eps),
+          _dt(gate), _stream())
+    return out
+
+
+# ------------------------------------------------------------------------------ attention over a cached latent
+
+def latent_prepare(down: torch.Tensor, q0: int, q_rank: int, kv0: int, rank: int, rot: int, rotary_dim: int,
+                   q_gain: torch.Tensor, kv_gain: torch.Tensor, eps: float, cos: Optional[torch.Tensor],
+                   sin: Optional[torch.Tensor], positions: torch.Tensor, token_req: torch.Tensor,
+                   block_table: torch.Tensor, layer: torch.Tensor, page_size: int, write_kv: bool = True) -> torch.Tensor:
+    """From a token's row of the stacked down-projection ``down`` (the cache's dtype or float32): the RMS-normed query
+    latent (columns ``q0`` on, ``q_rank`` of them, gain ``q_gain``), returned as [tokens, q_rank] in the cache's
+    dtype; and into the token's cache row [rank + rot] of ``layer`` [pages, page_size * (rank + rot)] the RMS-normed
+    key/value latent (columns ``kv0`` on, gain ``kv_gain``) followed by the ``rot`` columns after it, the first
+    ``rotary_dim`` of them rotated in halves by the position's angles."""
+    _dev(down, q_gain, kv_gain, cos, sin, positions, token_req, block_table, layer)
+    tokens = down.shape[0]
+    if layer.dim() != 2 or layer.shape[1] != page_size * (rank + rot):
+        raise KernelError(f"latent_prepare: cache layer {tuple(layer.shape)} does not hold pages of {page_size} rows of {rank + rot}")
+    if q_gain.dtype != torch.float32 or kv_gain.dtype != torch.float32:
+        raise KernelError("latent_prepare: gains are float32")
+    if rotary_dim and (cos is None or cos.dtype != torch.float32 or cos.shape[-1] != rotary_dim // 2):
+        raise KernelError("rotation tables must be float32 [positions, rotary_dim / 2]")
+    cq = torch.empty((tokens, q_rank), dtype=layer.dtype, device=down.device)
+    _call("lily_latent_prepare", _p(down), _dt(down), down.stride(0), q0, q_rank, kv0, rank, rot, rotary_dim, _p(q_gain),
+          _p(kv_gain), float(eps), _p(cos), _p(sin), _i32(positions, "positions"), _i32(token_req, "token_req"),
+          _i32(block_table, "block_table"), block_table.shape[-1], _p(layer), page_size, int(write_kv), _p(cq), tokens,
+          _dt(layer), _stream())
+    return cq
+
+
+def latent_query(qa: torch.Tensor, q: torch.Tensor, heads: int, d: int, rank: int, rot: int, rotary_dim: int,
+                 cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor) -> torch.Tensor:
+    """The queries the attention over the latent takes, [tokens, heads * (rank + rot)] in ``q``'s dtype: for each head
+    ``qa[head, token]`` (its unrotated part carried into the latent's space, [heads, tokens, rank], ``q``'s dtype or
+    float32) followed by the last ``rot`` columns of the head in ``q`` [tokens, heads * (d + rot)], rotated."""
+    _dev(qa, q, cos, sin, positions)
+    tokens = q.shape[0]
+    if tuple(qa.shape) != (heads, tokens, rank) or q.shape[1] != heads * (d + rot):
+        raise KernelError(f"latent_query: qa {tuple(qa.shape)}, q {tuple(q.shape)}")
+    out = torch.empty((tokens, heads * (rank + rot)), dtype=q.dtype, device=q.device)
+    _call("lily_latent_query", _p(qa), _dt(qa), _p(q), tokens, heads, d, rank, rot, rotary_dim, _p(cos), _p(sin),
+          _i32(positions, "positions"), _p(out), _dt(q), _stream())
+    return out
+
+
+def head_gate(ov: torch.Tensor, gate_rows: torch.Tensor, g0: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``out[t, h * dv + j] = ov[h, t, j] * sigmoid(gate_rows[t, g0 + h])``: ``ov`` [heads, tokens, dv]."""
+    _dev(ov, gate_rows)
+    heads, tokens, dv = ov.shape
+    out = torch.empty((tokens, heads * dv), dtype=out_dtype, device=ov.device)
+    _call("lily_head_gate", _p(ov), _dt(ov), _p(gate_rows), _dt(gate_rows), gate_rows.stride(0), g0, tokens, heads, dv,
+          _p(out), _dt(out), _stream())
+    return out
+
+
+# ------------------------------------------------------------------------------ routed experts
+
+@dataclass
+class ExpertRouting:
+    """A step's routing for one layer, all on the device: ``chosen`` / ``weights`` [tokens, top]; the pairs (token, choice)
+    of experts that have weights grouped by expert (``offsets``, ``order``, ``place``) and the tiles the grouped
+    products run over."""
+
+    chosen: torch.Tensor
+    weights: torch.Tensor
+    offsets: torch.Tensor
+    order: torch.Tensor
+    place: torch.Tensor
+    tile_expert: torch.Tensor
+    tile_row: torch.Tensor
+    tile_count: torch.Tensor
+    max_tiles: int
+    top: int
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: int, experts: int) -> ExpertRouting:
+    """Softmax scores over all router outputs (float32 logits ``router . h``), the ``top`` largest scores + correction
+    chosen, their weights the scores themselves over their sum; then the pairs of the first ``experts`` outputs (those
+    with weights; the rest stand for the identity) grouped by expert."""
+    _dev(h, router, correction)
+    tokens, width = h.shape
+    outputs = router.shape[0]
+    if router.dtype != torch.float32 or correction.dtype != torch.float32 or router.shape[1] != width or correction.numel() != outputs:
+        raise KernelError("moe_route: router [outputs, width] and correction [outputs] are float32")
+    dev = h.device
+    pairs = tokens * top
+    tile_rows = int(library().lily_moe_tile_rows())
+    max_tiles = -(-pairs // tile_rows) + experts
+    ints = torch.empty(3 * pairs + experts + 1 + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
+    chosen, order, place, offsets, tile_expert, tile_row, tile_count = torch.split(
+        ints, [pairs, pairs, pairs, experts + 1, max_tiles, max_tiles, 1])
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=dev)
+    _call("lily_moe_route", _p(h), tokens, width, _p(router), _p(correction), outputs, top, _p(chosen), _p(weights), _dt(h),
+          _stream())
+    _call("lily_moe_align", _p(chosen), pairs, experts, _p(offsets), _p(order), _p(place), _p(tile_expert), _p(tile_row),
+          _p(tile_count), max_tiles, _stream())
+    return ExpertRouting(chosen.view(tokens, top), weights, offsets, order, place, tile_expert, tile_row, tile_count,
+                         max_tiles, top)
+
+
+def moe_experts(h: torch.Tensor, routing: ExpertRouting, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float,
+                alpha: float) -> torch.Tensor:
+    """The chosen experts' outputs summed with their weights, float32 [tokens, width].  ``w_gate_up`` [experts, 2 ff,
+    width] (an expert's gate rows, then its up rows), ``w_down`` [experts, width, ff].  An expert computes
+    ``W_down (g sigmoid(alpha g) (u + 1))`` with ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -limit, limit)``; a
+    choice beyond the experts that have weights contributes ``h`` itself."""
+    _dev(h, w_gate_up, w_down)
+    tokens, width = h.shape
+    r = routing
+    pairs = tokens * r.top
+    experts = w_down.shape[0] if w_down.dim() == 3 else 0
+    ff = w_down.shape[2] if experts else 0
+    y = torch.empty((max(pairs, 1), width), dtype=torch.float32, device=h.device)
+    if experts:
+        if w_gate_up.dtype != h.dtype or w_down.dtype != h.dtype or tuple(w_gate_up.shape) != (experts, 2 * ff, width):
+            raise KernelError(f"moe_experts: weights {tuple(w_gate_up.shape)} / {tuple(w_down.shape)} {w_down.dtype} for inputs {tuple(h.shape)} {h.dtype}")
+        act = torch.empty((max(pairs, 1), ff), dtype=h.dtype, device=h.device)
+        _call("lily_moe_gemm", 0, _p(h), h.stride(0), _p(w_gate_up), ff, width, _p(r.offsets), _p(r.order), r.top,
+              _p(r.tile_expert), _p(r.tile_row), _p(r.tile_count), r.max_tiles, _p(act), float(limit), float(alpha), _dt(h),
+              _stream())
+        _call("lily_moe_gemm", 1, _p(act), ff, _p(w_down), width, ff, _p(r.offsets), _p(r.order), r.top, _p(r.tile_expert),
+              _p(r.tile_row), _p(r.tile_count), r.max_tiles, _p(y), 0.0, 0.0, _dt(h), _stream())
+    out = torch.empty((tokens, width), dtype=torch.float32, device=h.device)
+    _call("lily_moe_combine", _p(y), _p(h), _p(r.place), _p(r.weights), tokens, r.top, width, _p(out), _dt(h), _stream())
     return out
 
 

@@ -1,0 +1,286 @@
+// A linear-attention mixer with a decay that depends on the data (the "wkv" recurrence of the RWKV family):
+// token shift, the decay's logarithm, and the recurrence itself.
+//
+// Per request the state lives in one float32 row of a slot table: first the heads' matrices
+// [heads, d (key), d (value)], then the mixer's input at the request's last token [width] (the token shift of the
+// next step reads it).  A row is zero when its request starts.
+//
+//   token shift   m_s[t] = h[t] + (h[t - 1] - h[t]) * mu_s            for each of S streams (r, k, v, g, w)
+//   decay         lw[t, c] = -exp(w0[c] + sum_j W2[c, j] tanh(a[t, j]))  (the decay's logarithm; decay = exp(lw))
+//   recurrence    o_t[j] = sum_i r_t[i] (S[i, j] + u[i] k_t[i] v_t[j]);   S[i, j] <- exp(lw_t[i]) S[i, j] + k_t[i] v_t[j]
+//
+// Decays, their logarithms, the state and the sums over it are float32 in both precisions.
+#include "common.cuh"
+
+namespace lily {
+
+// ---------------------------------------------------------------------------- token shift
+
+// grid (tokens, ceil(width / 256)), block 256: a thread owns one column of one token.  The thread of a request's
+// first new token reads the carried input from the slot and is the one that writes the new one (the input at the
+// request's last new token), so nothing it reads is written by another thread of the launch.
+template <typename T>
+__global__ void token_shift_mix_kernel(const T* __restrict__ h, int tokens, int width, const float* __restrict__ mu,
+                                       int streams, float* __restrict__ state, size_t state_stride, size_t state_off,
+                                       const int* __restrict__ cu_seqlens, const int* __restrict__ token_req,
+                                       const int* __restrict__ slots, T* __restrict__ out) {
+    pdl_enter_small();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const int r = token_req[t];
+    const int first = cu_seqlens[r];
+    const float cur = to_float(h[(size_t)t * width + c]);
+    float prev;
+    if (t == first) {
+        float* st = state + (size_t)slots[r] * state_stride + state_off + c;
+        prev = *st;
+        *st = to_float(h[(size_t)(cu_seqlens[r + 1] - 1) * width + c]);
+    } else {
+        prev = to_float(h[(size_t)(t - 1) * width + c]);
+    }
+    const float diff = prev - cur;
+    for (int s = 0; s < streams; ++s)
+        out[((size_t)s * tokens + t) * width + c] = from_float<T>(fmaf(diff, mu[(size_t)s * width + c], cur));
+}
+
+// ---------------------------------------------------------------------------- the decay's logarithm
+
+// grid (tokens, ceil(cols / 128)), block 128; a [tokens, rank] float32, w2t [rank, cols] float32 (the second
+// matrix of the low-rank pair, transposed so that neighbouring threads read neighbouring numbers), w0 [cols].
+__global__ void wkv_decay_kernel(const float* __restrict__ a, int rank, const float* __restrict__ w2t,
+                                 const float* __restrict__ w0, int cols, float* __restrict__ lw) {
+    extern __shared__ float th[];          // tanh(a[t, :])
+    pdl_enter_small();
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(a[(size_t)t * rank + j]);
+    __syncthreads();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float z = 0.f;
+    for (int j = 0; j < rank; ++j) z = fmaf(th[j], w2t[(size_t)j * cols + c], z);
+    lw[(size_t)t * cols + c] = -expf(z + w0[c]);
+}
+
+// ---------------------------------------------------------------------------- the recurrence
+
+// grid (heads, requests, column blocks), block ceil(d / PC) * ks threads (whole warps, at most 256: wider heads are
+// cut by value columns over the third grid axis): `ks` neighbouring lanes share
+// PC neighbouring value columns of the head's matrix and hold NPT of its key rows each in registers (rows
+// lane * NPT ... of a padded count ks * NPT >= d), so that one r, k and decay read from shared memory serve 2 * PC
+// multiply-adds.  The tokens of the request run one after another, staged TT at a time in shared memory.
+constexpr int WKV_NPT = 16, WKV_PC = 4, WKV_TT = 16, WKV_PAD = 4;
+
+template <typename T>
+__global__ void wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
+                                const float* __restrict__ lw, const float* __restrict__ u, float* __restrict__ state,
+                                size_t state_stride, float* __restrict__ y, const int* __restrict__ cu_seqlens,
+                                const int* __restrict__ slots, int heads, int d, int ks) {
+    extern __shared__ __align__(16) float sm[];
+    const int rows = ks * (WKV_NPT + WKV_PAD);              // floats of one token's r (or k, or decay) in shared memory
+    float* rs = sm;                                          // [TT][rows]
+    float* kk = rs + WKV_TT * rows;
+    float* ws = kk + WKV_TT * rows;
+    float* vs = ws + WKV_TT * rows;                          // [TT][d]
+    float* bonus = vs + WKV_TT * d;                          // [TT]: sum_i r[i] u[i] k[i]
+    float* us = bonus + WKV_TT;                              // [d]
+    pdl_enter_small();
+    const int head = blockIdx.x, req = blockIdx.y;
+    const int tok0 = cu_seqlens[req], n = cu_seqlens[req + 1] - tok0;
+    if (n <= 0) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    const int part = tid % ks, col0 = (blockIdx.z * (blockDim.x / ks) + tid / ks) * WKV_PC;  // this thread's key rows and value columns
+    const bool live = col0 < d;
+    const int hd = heads * d;
+    float* st = state + (size_t)slots[req] * state_stride + (size_t)head * d * d;
+    float S[WKV_NPT][WKV_PC];
+#pragma unroll
+    for (int i = 0; i < WKV_NPT; ++i) {
+        const int row = part * WKV_NPT + i;
+#pragma unroll
+        for (int c = 0; c < WKV_PC; ++c)
+            S[i][c] = (live && row < d && col0 + c < d) ? st[(size_t)row * d + col0 + c] : 0.f;
+    }
+    for (int i = tid; i < d; i += blockDim.x) us[i] = u[(size_t)head * d + i];
+    // rows beyond d read zeros for r and k, so the padded entries of S stay zero and add nothing
+    for (int i = tid; i < WKV_TT * rows; i += blockDim.x) { rs[i] = 0.f; kk[i] = 0.f; ws[i] = 0.f; }
+
+    for (int t0 = 0; t0 < n; t0 += WKV_TT) {
+        const int tt = min(WKV_TT, n - t0);
+        __syncthreads();
+        for (int i = tid; i < tt * d; i += blockDim.x) {
+            const int t = i / d, c = i - t * d;
+            const size_t src = (size_t)(tok0 + t0 + t) * in_stride + (size_t)head * d + c;
+            const int at = t * rows + (c / WKV_NPT) * (WKV_NPT + WKV_PAD) + c % WKV_NPT;
+            rs[at] = to_float(r[src]);
+            kk[at] = to_float(k[src]);
+            vs[t * d + c] = to_float(v[src]);
+            ws[at] = expf(lw[(size_t)(tok0 + t0 + t) * hd + (size_t)head * d + c]);
+        }
+        __syncthreads();
+        for (int t = warp; t < tt; t += nwarp) {
+            float b = 0.f;
+            for (int c = lane; c < d; c += 32) {
+                const int at = t * rows + (c / WKV_NPT) * (WKV_NPT + WKV_PAD) + c % WKV_NPT;
+                b = fmaf(rs[at] * us[c], kk[at], b);
+            }
+            b = warp_sum(b);
+            if (lane == 0) bonus[t] = b;
+        }
+        __syncthreads();
+        for (int t = 0; t < tt; ++t) {
+            float vv[WKV_PC], acc[WKV_PC];
+#pragma unroll
+            for (int c = 0; c < WKV_PC; ++c) {
+                vv[c] = (live && col0 + c < d) ? vs[t * d + col0 + c] : 0.f;
+                acc[c] = 0.f;
+            }
+            const float* rp = rs + t * rows + part * (WKV_NPT + WKV_PAD);
+            const float* kp = kk + t * rows + part * (WKV_NPT + WKV_PAD);
+            const float* wp = ws + t * rows + part * (WKV_NPT + WKV_PAD);
+#pragma unroll
+            for (int i = 0; i < WKV_NPT; i += 4) {
+                const float4 r4 = *reinterpret_cast<const float4*>(rp + i);
+                const float4 k4 = *reinterpret_cast<const float4*>(kp + i);
+                const float4 w4 = *reinterpret_cast<const float4*>(wp + i);
+                const float rr[4] = {r4.x, r4.y, r4.z, r4.w}, kq[4] = {k4.x, k4.y, k4.z, k4.w}, wq[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+#pragma unroll
+                    for (int c = 0; c < WKV_PC; ++c) {
+                        acc[c] = fmaf(rr[e], S[i + e][c], acc[c]);
+                        S[i + e][c] = fmaf(wq[e], S[i + e][c], kq[e] * vv[c]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < WKV_PC; ++c) {
+                for (int o = 1; o < ks; o <<= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+            }
+            if (live && part == 0) {
+                const float bt = bonus[t];
+                float* dst = y + (size_t)(tok0 + t0 + t) * hd + (size_t)head * d + col0;
+#pragma unroll
+                for (int c = 0; c < WKV_PC; ++c)
+                    if (col0 + c < d) dst[c] = fmaf(bt, vv[c], acc[c]);
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < WKV_NPT; ++i) {
+            const int row = part * WKV_NPT + i;
+#pragma unroll
+            for (int c = 0; c < WKV_PC; ++c)
+                if (row < d && col0 + c < d) st[(size_t)row * d + col0 + c] = S[i][c];
+        }
+    }
+}
+
+
+// ---------------------------------------------------------------------------- unit norm by head, gain, gate
+
+// out[t, c] = y[t, c] / rms(y[t, head of c]) * gain[c] * silu(g[t, c]): each group of `gsize` columns is divided by
+// its own root mean square; the gate multiplies the normed value.  grid (tokens, ceil(groups / 4)), block 128: a
+// warp owns one group of one token.
+template <typename T>
+__global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const T* __restrict__ g, int g_stride,
+                                          const float* __restrict__ gain, T* __restrict__ out, int inner, int gsize,
+                                          int groups, float eps) {
+    pdl_enter_small();
+    const size_t t = blockIdx.x;
+    const int lane = threadIdx.x & 31, grp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (grp >= groups) return;
+    const int c0 = grp * gsize;
+    const float* yr = y + t * inner + c0;
+    float ssq = 0.f;
+    for (int i = lane; i < gsize; i += 32) ssq = fmaf(yr[i], yr[i], ssq);
+    const float inv = rsqrtf(warp_sum(ssq) / (float)gsize + eps);
+    const T* gr = g + t * g_stride + c0;
+    T* dst = out + t * inner + c0;
+    for (int i = lane; i < gsize; i += 32) {
+        const float z = to_float(gr[i]);
+        dst[i] = from_float<T>(((yr[i] * inv) * gain[c0 + i]) * (z / (1.f + expf(-z))));
+    }
+}
+
+}  // namespace lily
+
+using namespace lily;
+
+LILY_API int lily_token_shift_mix(const void* h, int tokens, int width, const float* mu, int streams, float* state,
+                                  size_t state_stride, size_t state_off, const int* cu_seqlens, const int* token_req,
+                                  const int* slots, void* out, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LILY_REQUIRE(width > 0 && streams > 0, "token_shift_mix: width=%d streams=%d", width, streams);
+    dim3 grid(tokens, (width + 255) / 256), block(256);
+    LILY_REQUIRE(grid.y <= 65535, "token_shift_mix: width %d", width);
+    if (dtype == kBF16)
+        launch_pdl(token_shift_mix_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)h, tokens, width, mu,
+                   streams, state, state_stride, state_off, cu_seqlens, token_req, slots, (__nv_bfloat16*)out);
+    else
+        launch_pdl(token_shift_mix_kernel<float>, grid, block, 0, stream, (const float*)h, tokens, width, mu, streams, state,
+                   state_stride, state_off, cu_seqlens, token_req, slots, (float*)out);
+    LILY_CHECK_LAUNCH("token_shift_mix");
+    return 0;
+}
+
+LILY_API int lily_wkv_decay(const float* a, int tokens, int rank, const float* w2t, const float* w0, int cols, float* lw,
+                            cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LILY_REQUIRE(rank > 0 && cols > 0 && rank <= 8192, "wkv_decay: rank=%d cols=%d", rank, cols);
+    dim3 grid(tokens, (cols + 127) / 128), block(128);
+    LILY_REQUIRE(grid.y <= 65535, "wkv_decay: %d columns", cols);
+    launch_pdl(wkv_decay_kernel, grid, block, (size_t)rank * sizeof(float), stream, a, rank, w2t, w0, cols, lw);
+    LILY_CHECK_LAUNCH("wkv_decay");
+    return 0;
+}
+
+LILY_API int lily_wkv_max_head_dim() { return 256; }
+
+LILY_API int lily_wkv_scan(const void* r, const void* k, const void* v, int in_stride, const float* lw, const float* u,
+                           float* state, size_t state_stride, float* y, const int* cu_seqlens, const int* slots,
+                           int requests, int heads, int d, int dtype, cudaStream_t stream) {
+    if (requests == 0) return 0;
+    LILY_REQUIRE(heads > 0 && d > 0 && d <= 256, "wkv_scan: %d heads of size %d (sizes up to 256)", heads, d);
+    LILY_REQUIRE(requests <= 65535, "wkv_scan: %d heads, %d requests", heads, requests);
+    int ks = 1;
+    while (ks * WKV_NPT < d) ks <<= 1;
+    const int groups = (d + WKV_PC - 1) / WKV_PC;                       // groups of PC value columns
+    int threads = (groups * ks + 31) / 32 * 32;
+    if (threads > 256) threads = 256;
+    const int per_block = threads / ks;
+    const size_t smem = sizeof(float) * ((size_t)3 * WKV_TT * ks * (WKV_NPT + WKV_PAD) + (size_t)WKV_TT * d + WKV_TT + d);
+    dim3 grid(heads, requests, (groups + per_block - 1) / per_block), block(threads);
+#define GO(T)                                                                                                         \
+    do {                                                                                                              \
+        static size_t granted = 48 * 1024;                                                                            \
+        if (smem > granted) {                                                                                         \
+            cudaError_t e = cudaFuncSetAttribute(wkv_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) { set_error("wkv_scan: cannot get %zu bytes of shared memory", smem); return 2; }    \
+            granted = smem;                                                                                           \
+        }                                                                                                             \
+        launch_pdl(wkv_scan_kernel<T>, grid, block, smem, stream, (const T*)r, (const T*)k, (const T*)v, in_stride, lw, u, \
+                   state, state_stride, y, cu_seqlens, slots, heads, d, ks);                                          \
+    } while (0)
+    if (dtype == kBF16) GO(__nv_bfloat16); else GO(float);
+#undef GO
+    LILY_CHECK_LAUNCH("wkv_scan");
+    return 0;
+}
+
+LILY_API int lily_group_rmsnorm_gate(const float* y, const void* g, int g_stride, const float* gain, void* out, int tokens,
+                                     int inner, int groups, float eps, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LILY_REQUIRE(groups >= 1 && inner % groups == 0, "group_rmsnorm_gate: %d columns in %d groups", inner, groups);
+    dim3 grid(tokens, (groups + 3) / 4), block(128);
+    LILY_REQUIRE(grid.y <= 65535, "group_rmsnorm_gate: %d groups", groups);
+    if (dtype == kBF16)
+        launch_pdl(group_rmsnorm_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, y, (const __nv_bfloat16*)g, g_stride, gain,
+                   (__nv_bfloat16*)out, inner, inner / groups, groups, eps);
+    else
+        launch_pdl(group_rmsnorm_gate_kernel<float>, grid, block, 0, stream, y, (const float*)g, g_stride, gain, (float*)out,
+                   inner, inner / groups, groups, eps);
+    LILY_CHECK_LAUNCH("group_rmsnorm_gate");
+    return 0;
+}

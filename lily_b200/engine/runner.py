@@ -238,7 +238,11 @@ class ModelRunner:
         cfg, gen = read_model_dir(args.model_path)
         arch = resolve_architecture(architecture_names(cfg))
         config = arch.config_from_dict(cfg, gen, architecture=arch.name)
-        return cls(arch.build_spec(config), CheckpointSource(args.model_path), args, ops)
+        source = CheckpointSource(args.model_path)
+        if hasattr(config, "sizes_from_tensors"):
+            # sizes that config.json leaves to the checkpoint are read off its tensors' shapes (headers only)
+            config = config.sizes_from_tensors({name: tuple(shape) for name, (_, shape) in source.entries().items()})
+        return cls(arch.build_spec(config), source, args, ops)
 
     @classmethod
     def from_random(cls, config_json: Dict[str, Any], seed: int, args: ServerArgs, ops: Any = None,

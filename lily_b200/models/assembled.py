@@ -27,6 +27,14 @@ class AssembledModel:
         self.spec, self.ctx = spec, ctx
         self.blocks = [build_part("block", b, b.prefix, ctx) for b in spec.blocks]
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix, ctx)
+        self.embed_norm = None if spec.embed_norm is None else build_part("norm", spec.embed_norm, spec.embed_norm_prefix, ctx)
+        # vectors added to the stream ahead of a run of the schedule: tensor name -> rows the schedule names
+        self.step_rows: Dict[str, int] = {}
+        for entry in spec.schedule:
+            if entry.step is not None:
+                name, row = entry.step
+                self.step_rows[name] = max(self.step_rows.get(name, 0), int(row) + 1)
+        self.step_vectors: Dict[str, torch.Tensor] = {}
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
 
@@ -93,6 +101,10 @@ class AssembledModel:
         for b in self.blocks:
             out.update(b.tensors())
         out.update(self.final_norm.tensors())
+        if self.embed_norm is not None:
+            out.update(self.embed_norm.tensors())
+        for name, rows in self.step_rows.items():
+            out[name] = TensorSpec((rows, s.hidden_size), role="vector", init="normal")
         if s.head_name is not None:
             out[s.head_name] = TensorSpec((s.vocab_size, s.hidden_size), short_rows=True)
         return out
@@ -108,6 +120,9 @@ class AssembledModel:
         for b in self.blocks:
             b.load(get)
         self.final_norm.load(get)
+        if self.embed_norm is not None:
+            self.embed_norm.load(get)
+        self.step_vectors = {name: get(name).float().contiguous() for name in self.step_rows}      # added in float32
         self.head = self.embed if self.spec.head_name is None else get(self.spec.head_name).contiguous()
 
     def weight_bytes(self) -> int:
@@ -124,6 +139,8 @@ class AssembledModel:
             for part in b.parts:
                 visit(part)
         visit(self.final_norm)
+        if self.embed_norm is not None:
+            visit(self.embed_norm)
         return total
 
     # ---- one step ------------------------------------------------------------------
@@ -133,13 +150,17 @@ class AssembledModel:
         ``[len(batch.logit_rows), vocab]``."""
         ops, spec = self.ctx.ops, self.spec
         residual = ops.embed(self.embed, batch.token_ids, future=batch.future_tokens, scale=spec.embed_scale)
+        if self.embed_norm is not None:
+            # the stream starts as the normalised embedding rows, float32 like every later sum into it
+            residual = self.embed_norm.forward(residual, None, write_residual=False, out_dtype=torch.float32)
         delta = None
         for pos, entry in enumerate(spec.schedule):
             caches = [LayerCache(ec[0], cache.groups[ec[0]].data[ec[1]]) if ec is not None else None
                       for ec in self.entry_cache[pos]]
             states = [cache.states[es] if es is not None else None for es in self.entry_state[pos]]
             writes = all(ec[2] for ec in self.entry_cache[pos] if ec is not None)
-            delta = self.blocks[entry.block].forward(residual, delta, batch, RunSlots(caches, states, writes))
+            bias = self.step_vectors[entry.step[0]][entry.step[1]] if entry.step is not None else None
+            delta = self.blocks[entry.block].forward(residual, delta, batch, RunSlots(caches, states, writes, bias))
         if batch.logit_rows.numel() == 0:
             return torch.empty((0, spec.vocab_size), dtype=torch.float32, device=residual.device)
         x = self.final_norm.forward(residual, delta, rows=batch.logit_rows)

@@ -29,7 +29,7 @@ Interfaces
 ``Norm.forward(residual, delta, delta_bias, rows, write_residual)`` -> normed activations.
 ``Block.mixers``     -> the mixers of the block, in a fixed order; each run of the block gets a
                         cache layer and a state tensor for each of them (``RunSlots``).
-``Block.forward(residual, delta, batch, run)`` -> next pending delta.
+``Block.forward(residual, delta, batch, run)`` -> next pending delta (a tensor, or a tuple of tensors to be summed).
 """
 
 from __future__ import annotations
@@ -74,6 +74,8 @@ class CacheNeed:
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None     # the values' head size where it differs from the keys' (None: head_dim)
+    values_in_keys: bool = False         # the values are columns of the key rows themselves (a cached latent that serves
+                                         # as both): a page holds keys only
 
 
 @dataclass(frozen=True)
@@ -142,6 +144,8 @@ class RunSlots:
     caches: List[Any]
     states: List[Any]
     write_cache: bool = True
+    stream_bias: Optional[torch.Tensor] = None      # a float32 vector the run adds to every row of the stream before
+                                                    # anything else (``ScheduleEntry.step``); the block's first norm adds it
 
 
 class Block(Part):
@@ -197,7 +201,7 @@ def _load_builtin_parts() -> None:
     global _BUILTINS
     if not _BUILTINS:
         _BUILTINS = True
-        from lily_b200.parts import attention, block, mlp, norm, rope, ssm  # noqa: F401
+        from lily_b200.parts import attention, block, experts, latent_attention, mlp, norm, rope, ssm, wkv  # noqa: F401
 
 
 # --------------------------------------------------------------------------- model description
@@ -226,6 +230,9 @@ class ScheduleEntry:
 
     block: int
     reads: Optional[int] = None
+    # (tensor name, row): row ``row`` of the checkpoint tensor ``name`` [rows, hidden] is added to the residual stream
+    # ahead of this run (a stretch of blocks that runs several times over with a learned vector ahead of each pass)
+    step: Optional[Tuple[str, int]] = None
 
 
 @dataclass
@@ -248,3 +255,5 @@ class ModelSpec:
     embed_scale: float = 1.0                          # the embedding rows are multiplied by this
     logit_scale: float = 1.0                          # logits = logit_scale * (x . head^T) ...
     logit_softcap: Optional[float] = None             # ... then cap * tanh(. / cap) when given
+    embed_norm: Any = None                            # a norm spec: the embedding rows are normalised before the first block
+    embed_norm_prefix: str = "embed.norm"

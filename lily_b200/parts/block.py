@@ -37,7 +37,7 @@ class PreNormBlock(Block):
             part.load(get)
 
     def forward(self, residual, delta, batch, run: RunSlots):
-        x = self.norm_in.forward(residual, delta)
+        x = self.norm_in.forward(residual, delta, delta_bias=run.stream_bias)
         a = self.mixer.forward(x, batch, run.caches[0], run.states[0], run.write_cache)
         y = self.norm_post.forward(residual, a)
         return self.feed_forward.forward(y, batch)
@@ -48,7 +48,10 @@ class ParallelBlockSpec:
     """One norm whose output every sublayer reads: ``h = norm(r)``, ``r += mean_k(rms(mixer_k(h)) * gain_k) + ff(h)``.
     ``mixers`` lists (name under the block's prefix, mixer spec, name of the mixer's output gain); the feed-forward
     may be absent.  The mixers run side by side on the same ``h``; each output is divided by its root mean square
-    over the model width (``eps``) and multiplied by its own gain before the mean is taken."""
+    over the model width (``eps``) and multiplied by its own gain before the mean is taken.
+    A gain name of None leaves the mixer's output as it is (one mixer then: ``r += mixer(h) + ff(.)``, the sum formed
+    in float32 by the next residual add).  ``ff_norm`` gives the feed-forward a norm of its own over the same ``r``
+    (``r += mixer(norm(r)) + ff(ff_norm(r))``); both norms share one pass over the rows."""
 
     prefix: str
     hidden_size: int
@@ -59,6 +62,8 @@ class ParallelBlockSpec:
     kind: str = "parallel"
     norm_name: str = "norm1"
     feed_forward_name: str = "mlp"
+    ff_norm: Any = None
+    ff_norm_name: str = "norm2"
 
 
 @register_part("block", "parallel")
@@ -72,8 +77,16 @@ class ParallelBlock(Block):
         self.mixers = tuple(build_part("mixer", m, f"{p}.{name}", ctx) for name, m, _ in spec.mixers)
         self.feed_forward = None if spec.feed_forward is None else \
             build_part("feed_forward", spec.feed_forward, f"{p}.{spec.feed_forward_name}", ctx)
-        self.parts = (self.norm, *self.mixers) + ((self.feed_forward,) if self.feed_forward is not None else ())
-        self.gain_names = [f"{p}.{gain}" for _, _, gain in spec.mixers]
+        self.ff_norm = None
+        if spec.ff_norm is not None and self.feed_forward is not None:
+            self.ff_norm = build_part("norm", spec.ff_norm, f"{p}.{spec.ff_norm_name}", ctx)
+        self.parts = (self.norm, *self.mixers) + ((self.feed_forward,) if self.feed_forward is not None else ()) + \
+            ((self.ff_norm,) if self.ff_norm is not None else ())
+        plain = [gain is None for _, _, gain in spec.mixers]
+        if any(plain) and (not all(plain) or len(plain) != 1):
+            raise ValueError("a parallel block takes its mixers' outputs as they are only when it has one mixer")
+        self.plain_sum = all(plain)
+        self.gain_names = [] if self.plain_sum else [f"{p}.{gain}" for _, _, gain in spec.mixers]
         self.gains = []
 
     def tensors(self) -> Dict[str, TensorSpec]:
@@ -90,8 +103,13 @@ class ParallelBlock(Block):
         self.gains = [get(name).float().contiguous() for name in self.gain_names]
 
     def forward(self, residual, delta, batch, run: RunSlots):
-        h = self.norm.forward(residual, delta)
+        if self.ff_norm is not None:
+            h, h_ff = self.norm.forward(residual, delta, delta_bias=run.stream_bias, also=self.ff_norm)
+        else:
+            h = h_ff = self.norm.forward(residual, delta, delta_bias=run.stream_bias)
         outs = [m.forward(h, batch, run.caches[k], run.states[k], run.write_cache) for k, m in enumerate(self.mixers)]
-        f = self.feed_forward.forward(h, batch) if self.feed_forward is not None else None
+        f = self.feed_forward.forward(h_ff, batch) if self.feed_forward is not None else None
+        if self.plain_sum:
+            return (outs[0], f) if f is not None else outs[0]          # summed in float32 by the next residual add
         # float32, as one plane of partial sums: the next norm adds it into the residual stream
         return self.ctx.ops.normed_mean(outs, self.gains, self.spec.eps, add=f)

@@ -20,6 +20,8 @@ class RMSNormSpec:
     eps: float
     kind: str = "rmsnorm"
     suffix: str = ".weight"        # the gain's name is the part's prefix followed by this ("" where the prefix is the name)
+    offset: float = 0.0            # the checkpoint stores the gain minus this (1.0: gains stored around zero); the sum
+                                   # is formed once, in float32, when the gain is loaded
 
 
 @register_part("norm", "rmsnorm")
@@ -33,9 +35,23 @@ class RMSNorm(Norm):
 
     def load(self, get) -> None:
         self.weight = get(f"{self.prefix}{self.spec.suffix}")
+        if self.spec.offset:
+            self.weight = (self.weight.float() + self.spec.offset).contiguous()
 
-    def forward(self, residual, delta=None, delta_bias=None, rows=None, write_residual=True):
-        if delta_bias is not None:
-            raise NotImplementedError("rmsnorm takes no separate bias; add it in the producing linear")
-        return self.ctx.ops.add_rmsnorm(residual, delta, self.weight, self.spec.eps, self.ctx.dtype, rows=rows,
-                                        write_residual=write_residual)
+    def forward(self, residual, delta=None, delta_bias=None, rows=None, write_residual=True, also=None, out_dtype=None):
+        """``delta`` may be a tuple of tensors to be summed; ``delta_bias`` a float32 vector added to every row;
+        ``also`` another norm of this kind and size whose output of the same rows is wanted too (returns a pair)."""
+        deltas = [d for d in delta if d is not None] if isinstance(delta, (tuple, list)) else ([delta] if delta is not None else [])
+        if delta_bias is None and also is None and len(deltas) <= 1:
+            return self.ctx.ops.add_rmsnorm(residual, deltas[0] if deltas else None, self.weight, self.spec.eps,
+                                            out_dtype or self.ctx.dtype, rows=rows, write_residual=write_residual)
+        if rows is not None:
+            # gathered rows: the sum goes into the stream first, then the plain form reads the rows
+            self.ctx.ops.add_rmsnorm_multi(residual, deltas, [], self.spec.eps, self.ctx.dtype, bias=delta_bias)
+            return self.ctx.ops.add_rmsnorm(residual, None, self.weight, self.spec.eps, out_dtype or self.ctx.dtype, rows=rows)
+        if also is not None and (also.spec.eps != self.spec.eps or also.spec.size != self.spec.size):
+            raise ValueError("two norms share a pass over the rows only with one size and one eps")
+        gains = [self.weight.float()] + ([also.weight.float()] if also is not None else [])
+        outs = self.ctx.ops.add_rmsnorm_multi(residual, deltas, gains, self.spec.eps, out_dtype or self.ctx.dtype,
+                                              bias=delta_bias, write_residual=write_residual)
+        return outs if also is not None else outs[0]

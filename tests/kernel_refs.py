@@ -73,6 +73,19 @@ def add_rmsnorm(resid, delta, weight, eps, out_dtype, rows=None, write_residual=
     return ((v * torch.rsqrt(var + eps)) * weight.float()).to(out_dtype)
 
 
+def add_rmsnorm_multi(resid, deltas, gains, eps, out_dtype, bias=None, write_residual=True):
+    v = resid
+    for d in deltas:
+        if d is not None:
+            v = v + _sum(d).float()
+    if bias is not None:
+        v = v + bias.float()
+    if write_residual:
+        resid.copy_(v)
+    unit = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    return tuple((unit * g.float()).to(out_dtype) for g in gains)
+
+
 def silu_mul(gate_up, out_dtype=None, out=None, block=None, activation="silu"):
     out_dtype = out_dtype or gate_up.dtype
     gate_up = _sum(gate_up)
@@ -88,10 +101,13 @@ def silu_mul(gate_up, out_dtype=None, out=None, block=None, activation="silu"):
     return ((g / (1 + torch.exp(-g))) * u).to(out_dtype)
 
 
-def _pages(kv_layer, nkv, page_size, d, dv):
-    """Views of a cache layer's keys [pages, nkv, page, d] and values [pages, nkv, page, dv] (both layouts)."""
+def _pages(kv_layer, nkv, page_size, d, dv, values_in_keys=False):
+    """Views of a cache layer's keys [pages, nkv, page, d] and values [pages, nkv, page, dv] (all layouts)."""
     if kv_layer.dim() == 5:
         return kv_layer[:, 0], kv_layer[:, 1]
+    if values_in_keys:
+        keys = kv_layer.view(-1, nkv, page_size, d)
+        return keys, keys[..., :dv]
     cut = nkv * page_size * d
     return kv_layer[:, :cut].view(-1, nkv, page_size, d), kv_layer[:, cut:].view(-1, nkv, page_size, dv)
 
@@ -193,7 +209,7 @@ def uses_tensor_cores(dtype, d):
     return dtype == torch.bfloat16 and d in (64, 128, 192, 256)
 
 
-def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0, softcap=None, dv=None):
+def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0, softcap=None, dv=None, values_in_keys=False):
     return 32
 
 
@@ -216,7 +232,7 @@ class DecodePlan:
     stages: int = 0
 
 
-def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len, even=False, dv=None):
+def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len, even=False, dv=None, values_in_keys=False):
     if requests == 0:
         return DecodePlan(1, False, 0, "single")
     splits = 2 if max_seq_len >= 32 else 1
@@ -228,10 +244,10 @@ def decode_scratch_floats(requests, nq, d, splits):
     return requests * nq * splits * (d + 2) if splits > 1 else 0
 
 
-def _gather_kv(kv_layer, table_row, length, page_size, nkv=None, d=None, dv=None):
+def _gather_kv(kv_layer, table_row, length, page_size, nkv=None, d=None, dv=None, values_in_keys=False):
     pos = torch.arange(length, device=kv_layer.device)
     page = table_row[(pos // page_size)].long()
-    keys, values = _pages(kv_layer, nkv, page_size, d, dv)
+    keys, values = _pages(kv_layer, nkv, page_size, d, dv, values_in_keys)
     k = keys[page, :, pos % page_size]                 # [length, nkv, d]
     v = values[page, :, pos % page_size]
     return k.float(), v.float()
@@ -253,23 +269,24 @@ def _attend(q, k, v, q_pos, scale, window, softcap=None):
 
 
 def attention_prefill(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out, nq, nkv, d,
-                      page_size, scale, window=None, tile_rows=None, heads_per_block=0, softcap=None, dv=None):
+                      page_size, scale, window=None, tile_rows=None, heads_per_block=0, softcap=None, dv=None,
+                      values_in_keys=False):
     dv = dv or d
     for r in sorted(set(tile_req.tolist())):
         t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
         prefix = int(prefix_lens[r])
-        k, v = _gather_kv(kv_layer, block_table[r], prefix + t1 - t0, page_size, nkv, d, dv)
+        k, v = _gather_kv(kv_layer, block_table[r], prefix + t1 - t0, page_size, nkv, d, dv, values_in_keys)
         qpos = torch.arange(prefix, prefix + t1 - t0, device=q.device)
         o = _attend(q[t0:t1].float().view(-1, nq, d), k, v, qpos, scale, window, softcap)
         out[t0:t1] = o.reshape(t1 - t0, nq * dv).to(out.dtype)
 
 
 def attention_decode(q, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv, d, page_size, scale,
-                     window=None, stages=0, softcap=None, dv=None):
+                     window=None, stages=0, softcap=None, dv=None, values_in_keys=False):
     dv = dv or d
     for r in range(q.shape[0]):
         n = int(seq_lens[r])
-        k, v = _gather_kv(kv_layer, block_table[r], n, page_size, nkv, d, dv)
+        k, v = _gather_kv(kv_layer, block_table[r], n, page_size, nkv, d, dv, values_in_keys)
         o = _attend(q[r:r + 1].float().view(1, nq, d), k, v, torch.tensor([n - 1], device=q.device), scale, window, softcap)
         out[r] = o.reshape(nq * dv).to(out.dtype)
 
@@ -423,3 +440,124 @@ def top_logprobs(logits, k):
         tokens[r, :idx.numel()] = idx.to(torch.int32)
         logprobs[r, :idx.numel()] = lp[r, idx]
     return tokens, logprobs, counts
+
+
+# ---- per-head products, linear attention with a data-dependent decay, attention over a latent, routed experts
+
+def head_linear(x, weight, out_dtype=None):
+    """x [tokens, heads, k], weight [heads, n, k] -> [heads, tokens, n]."""
+    out = torch.einsum("thk,hnk->htn", x.float(), weight.float())
+    return out if (out_dtype == torch.float32 or x.dtype == torch.float32) else out.to(x.dtype)
+
+
+def token_shift_mix(h, mu, state, state_off, cu_seqlens, token_req, slots):
+    tokens, width = h.shape
+    prev = torch.empty((tokens, width), dtype=torch.float32, device=h.device)
+    for r in range(cu_seqlens.numel() - 1):
+        t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+        if t1 == t0:
+            continue
+        held = state[int(slots[r]), state_off:state_off + width]
+        prev[t0] = held
+        prev[t0 + 1:t1] = h[t0:t1 - 1].float()
+        held.copy_(h[t1 - 1].float())
+    cur = h.float()
+    return (cur[None] + (prev - cur)[None] * mu.float()[:, None, :]).to(h.dtype)
+
+
+def wkv_decay(a, w2t, w0):
+    return -torch.exp(torch.tanh(a.float()) @ w2t.float() + w0.float())
+
+
+def wkv_max_head_dim():
+    return 256
+
+
+def wkv_scan(r, k, v, log_decay, u, state, cu_seqlens, slots, requests, heads, d):
+    y = torch.empty((r.shape[0], heads * d), dtype=torch.float32, device=r.device)
+    for q in range(requests):
+        t0, t1 = int(cu_seqlens[q]), int(cu_seqlens[q + 1])
+        S = state[int(slots[q]), :heads * d * d].view(heads, d, d)
+        for t in range(t0, t1):
+            rt, kt, vt = (x[t].float().view(heads, d) for x in (r, k, v))
+            kv = kt[:, :, None] * vt[:, None, :]
+            y[t] = torch.einsum("hi,hij->hj", rt, S + u.float()[:, :, None] * kv).reshape(heads * d)
+            S.copy_(torch.exp(log_decay[t].float().view(heads, d))[:, :, None] * S + kv)
+    return y
+
+
+def group_rmsnorm_gate(y, gate, gain, groups, eps):
+    n, inner = y.shape
+    v = y.float().view(n, groups, inner // groups)
+    v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).reshape(n, inner)
+    z = gate.float()
+    return (v * gain.float() * (z * torch.sigmoid(z))).to(gate.dtype)
+
+
+def _rotate_halves(t, cos, sin, positions, rotary_dim):
+    if cos is None or not rotary_dim:
+        return t
+    half = rotary_dim // 2
+    shape = [t.shape[0]] + [1] * (t.dim() - 2) + [half]
+    c, s = cos[positions.long()].view(shape), sin[positions.long()].view(shape)
+    x1, x2, rest = t[..., :half], t[..., half:rotary_dim], t[..., rotary_dim:]
+    return torch.cat((x1 * c - x2 * s, x2 * c + x1 * s, rest), dim=-1)
+
+
+def latent_prepare(down, q0, q_rank, kv0, rank, rot, rotary_dim, q_gain, kv_gain, eps, cos, sin, positions, token_req,
+                   block_table, layer, page_size, write_kv=True):
+    x = down.float()
+    unit = lambda t: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)
+    cq = (unit(x[:, q0:q0 + q_rank]) * q_gain.float()).to(layer.dtype)
+    if write_kv:
+        latent = unit(x[:, kv0:kv0 + rank]) * kv_gain.float()
+        turned = _rotate_halves(x[:, kv0 + rank:kv0 + rank + rot], cos, sin, positions, rotary_dim)
+        pos = positions.long()
+        page = block_table[token_req.long(), pos // page_size].long()
+        rows = layer.view(-1, page_size, rank + rot)
+        rows[page, pos % page_size] = torch.cat([latent, turned], -1).to(layer.dtype)
+    return cq
+
+
+def latent_query(qa, q, heads, d, rank, rot, rotary_dim, cos, sin, positions):
+    tokens = q.shape[0]
+    turned = _rotate_halves(q.float().view(tokens, heads, d + rot)[..., d:], cos, sin, positions, rotary_dim)
+    return torch.cat([qa.float().transpose(0, 1), turned], -1).reshape(tokens, heads * (rank + rot)).to(q.dtype)
+
+
+def head_gate(ov, gate_rows, g0, out_dtype):
+    heads, tokens, dv = ov.shape
+    g = torch.sigmoid(gate_rows[:, g0:g0 + heads].float())                      # [tokens, heads]
+    return (ov.float().transpose(0, 1) * g[:, :, None]).reshape(tokens, heads * dv).to(out_dtype)
+
+
+@dataclass
+class ExpertRouting:
+    chosen: torch.Tensor
+    weights: torch.Tensor
+    top: int
+
+
+def moe_route(h, router, correction, top, experts):
+    s = torch.softmax(h.float() @ router.float().t(), -1)
+    chosen = torch.topk(s + correction.float(), top, dim=-1).indices
+    picked = torch.gather(s, 1, chosen)
+    return ExpertRouting(chosen.to(torch.int32), picked / (picked.sum(-1, keepdim=True) + 1e-20), top)
+
+
+def moe_experts(h, routing, w_gate_up, w_down, limit, alpha):
+    tokens, width = h.shape
+    experts = w_down.shape[0] if w_down.dim() == 3 else 0
+    ff = w_down.shape[2] if experts else 0
+    out = torch.zeros((tokens, width), dtype=torch.float32, device=h.device)
+    x = h.float()
+    for t in range(tokens):
+        for e, a in zip(routing.chosen[t].tolist(), routing.weights[t].tolist()):
+            if e < experts:
+                gu = w_gate_up[e].float() @ x[t]
+                g, u = gu[:ff].clamp(max=limit), gu[ff:].clamp(min=-limit, max=limit)
+                act = (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(h.dtype).float()
+                out[t] += a * (w_down[e].float() @ act)
+            else:
+                out[t] += a * x[t]
+    return out
