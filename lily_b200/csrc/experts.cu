@@ -226,6 +226,50 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
     out[(size_t)t * width + c] = acc;
 }
 
+
+// For the library's grouped product (bfloat16, many rows): the pairs' input rows in grouped order, and the activation
+// over its gate/up result.  grid (pairs), block 128; rows beyond offsets[experts] (pairs without weights) are zeroed
+// so that the product reads nothing unwritten.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ h, int width, const int* __restrict__ offsets, int experts,
+                                  const int* __restrict__ order, int top, T* __restrict__ out) {
+    pdl_wait();
+    const int row = blockIdx.x;
+    const bool live = row < offsets[experts];
+    const T* src = h + (size_t)(live ? order[row] / top : 0) * width;
+    T* dst = out + (size_t)row * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = live ? src[c] : from_float<T>(0.f);
+}
+
+// a[row, n] = g sigmoid(alpha g) (u + 1) from gu[row] = [gate (ff) | up (ff)], clamped as above.
+template <typename T>
+__global__ void moe_activation_kernel(const T* __restrict__ gu, int ff, T* __restrict__ a, float limit, float alpha) {
+    pdl_wait();
+    const size_t row = blockIdx.x;
+    for (int n = threadIdx.x; n < ff; n += blockDim.x) {
+        const float g = fminf(to_float(gu[row * 2 * ff + n]), limit);
+        const float u = fminf(fmaxf(to_float(gu[row * 2 * ff + ff + n]), -limit), limit);
+        a[row * ff + n] = from_float<T>((g / (1.f + expf(-alpha * g))) * (u + 1.f));
+    }
+}
+
+// out[t] = sum_k weight * (y[place] or h[t]) with y in the activation dtype (the library product's result)
+template <typename T>
+__global__ void moe_combine_rows_kernel(const T* __restrict__ y, const T* __restrict__ h, const int* __restrict__ place,
+                                        const float* __restrict__ weights, int top, int width, float* __restrict__ out) {
+    pdl_wait();
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const int at = place[(size_t)t * top + k];
+        const float w = weights[(size_t)t * top + k];
+        const float v = to_float(at >= 0 ? y[(size_t)at * width + c] : h[(size_t)t * width + c]);
+        acc = fmaf(w, v, acc);
+    }
+    out[(size_t)t * width + c] = acc;
+}
+
 }  // namespace lily
 
 using namespace lily;
@@ -287,5 +331,44 @@ LILY_API int lily_moe_combine(const float* y, const void* h, const int* place, c
     else
         launch_pdl(moe_combine_kernel<float>, grid, block, 0, stream, y, (const float*)h, place, weights, top, width, out);
     LILY_CHECK_LAUNCH("moe_combine");
+    return 0;
+}
+
+LILY_API int lily_moe_gather(const void* h, int width, const int* offsets, int experts, const int* order, int top, int pairs,
+                             void* out, int dtype, cudaStream_t stream) {
+    if (pairs == 0) return 0;
+    if (dtype == kBF16)
+        launch_pdl(moe_gather_kernel<__nv_bfloat16>, dim3(pairs), dim3(128), 0, stream, (const __nv_bfloat16*)h, width, offsets,
+                   experts, order, top, (__nv_bfloat16*)out);
+    else
+        launch_pdl(moe_gather_kernel<float>, dim3(pairs), dim3(128), 0, stream, (const float*)h, width, offsets, experts, order,
+                   top, (float*)out);
+    LILY_CHECK_LAUNCH("moe_gather");
+    return 0;
+}
+
+LILY_API int lily_moe_activation(const void* gu, int ff, int rows, void* a, float limit, float alpha, int dtype,
+                                 cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (dtype == kBF16)
+        launch_pdl(moe_activation_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, (const __nv_bfloat16*)gu, ff,
+                   (__nv_bfloat16*)a, limit, alpha);
+    else
+        launch_pdl(moe_activation_kernel<float>, dim3(rows), dim3(256), 0, stream, (const float*)gu, ff, (float*)a, limit, alpha);
+    LILY_CHECK_LAUNCH("moe_activation");
+    return 0;
+}
+
+LILY_API int lily_moe_combine_rows(const void* y, const void* h, const int* place, const float* weights, int tokens, int top,
+                                   int width, float* out, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    dim3 grid(tokens, (width + 255) / 256), block(256);
+    if (dtype == kBF16)
+        launch_pdl(moe_combine_rows_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)y, (const __nv_bfloat16*)h,
+                   place, weights, top, width, out);
+    else
+        launch_pdl(moe_combine_rows_kernel<float>, grid, block, 0, stream, (const float*)y, (const float*)h, place, weights, top,
+                   width, out);
+    LILY_CHECK_LAUNCH("moe_combine_rows");
     return 0;
 }

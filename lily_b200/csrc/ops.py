@@ -54,7 +54,8 @@ _SIGNATURES = {
     "lily_gemm_fp32_heads": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _sz, _sz, _vp],
     "lily_token_shift_mix": [_vp, _i, _i, _vp, _i, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _i, _vp],
     "lily_wkv_decay": [_vp, _i, _i, _vp, _vp, _i, _vp, _vp],
-    "lily_wkv_scan": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "lily_wkv_scan": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "lily_wkv_combine": [_vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lily_group_rmsnorm_gate": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "lily_latent_prepare": [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp,
                             _i, _i, _vp],
@@ -64,6 +65,9 @@ _SIGNATURES = {
     "lily_moe_align": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp],
     "lily_moe_gemm": [_i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _f, _f, _i, _vp],
     "lily_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp],
+    "lily_moe_gather": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp],
+    "lily_moe_activation": [_vp, _i, _i, _vp, _f, _f, _i, _vp],
+    "lily_moe_combine_rows": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp],
     "lily_argmax": [_vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_apply_penalties": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_top_logprobs": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
@@ -1033,15 +1037,66 @@ def wkv_max_head_dim() -> int:
     return int(library().lily_wkv_max_head_dim())
 
 
+WKV_CHUNK = 128         # tokens a chunk of a long portion
+WKV_DIRECT = 256        # portions up to this many tokens run in one piece, from and to the matrices in the slot
+
+
+@dataclass
+class WkvPlan:
+    """How a step's recurrence is cut: portions up to ``WKV_DIRECT`` tokens run whole; longer ones as chunks of
+    ``WKV_CHUNK`` tokens side by side (each first from zero, then, once ``wkv_combine`` has walked the chunks, from the
+    matrices it starts from).  The lists are device int32; ``short_cu`` / ``short_slots`` describe the short portions
+    as requests of their own."""
+
+    items: int
+    item_req: Optional[torch.Tensor]
+    item_start: Optional[torch.Tensor]
+    item_len: Optional[torch.Tensor]
+    longs: int
+    long_req: Optional[torch.Tensor]
+    long_first: Optional[torch.Tensor]
+    long_count: Optional[torch.Tensor]
+    short_reqs: Optional[torch.Tensor]      # requests that run whole (None: all of them)
+    shorts: int
+
+
+def wkv_plan(new_lens: Sequence[int], device) -> Optional[WkvPlan]:
+    """None when every portion runs whole."""
+    if not new_lens or max(new_lens) <= WKV_DIRECT:
+        return None
+    item_req, item_start, item_len, long_req, long_first, long_count, short = [], [], [], [], [], [], []
+    for r, n in enumerate(new_lens):
+        if n <= WKV_DIRECT:
+            short.append(r)
+            continue
+        long_req.append(r)
+        long_first.append(len(item_req))
+        long_count.append(-(-n // WKV_CHUNK))
+        for s0 in range(0, n, WKV_CHUNK):
+            item_req.append(r)
+            item_start.append(s0)
+            item_len.append(min(WKV_CHUNK, n - s0))
+    flat = torch.tensor(item_req + item_start + item_len + long_req + long_first + long_count + short, dtype=torch.int32)
+    flat = flat.to(device, non_blocking=True)
+    a, b = len(item_req), len(long_req)
+    parts = torch.split(flat, [a, a, a, b, b, b, len(short)])
+    return WkvPlan(a, parts[0], parts[1], parts[2], b, parts[3], parts[4], parts[5], parts[6] if short else None, len(short))
+
+
+def wkv_workspace_floats(plan: Optional[WkvPlan], heads: int, d: int) -> int:
+    return 0 if plan is None else plan.items * heads * (d * d + d)
+
+
 def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch.Tensor, u: torch.Tensor,
              state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, requests: int, heads: int,
-             d: int) -> torch.Tensor:
+             d: int, plan: Optional[WkvPlan] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The recurrence, a request's new tokens one after another from and to the head matrices in its slot (the first
     ``heads * d * d`` numbers of the row, [head, key row, value column]):
     ``o_t = (S + diag(u) k_t v_t^T)^T r_t``, then ``S <- diag(exp(log_decay_t)) S + k_t v_t^T``.
     ``r``, ``k``, ``v`` [tokens, heads * d] in the activation dtype (rows of equal stride), ``log_decay`` float32
-    [tokens, heads * d], ``u`` float32 [heads, d].  Returns float32 [tokens, heads * d]."""
-    _dev(log_decay, u, state, cu_seqlens, slots)
+    [tokens, heads * d], ``u`` float32 [heads, d].  Returns float32 [tokens, heads * d].  With a ``plan`` (``wkv_plan``)
+    and its ``workspace`` (float32, ``wkv_workspace_floats``) long portions run as chunks side by side."""
+    _dev(log_decay, u, state, cu_seqlens, slots, workspace)
     tokens = r.shape[0]
     stride = r.stride(0)
     for t in (r, k, v):
@@ -1052,8 +1107,24 @@ def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch
     if state.shape[1] < heads * d * d:
         raise KernelError("wkv_scan: the state row is too short for the head matrices")
     y = torch.empty((tokens, heads * d), dtype=torch.float32, device=r.device)
-    _call("lily_wkv_scan", _p(r), _p(k), _p(v), stride, _p(log_decay), _p(u), _p(state), state.stride(0), _p(y),
-          _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), requests, heads, d, _dt(r), _stream())
+    common = (_p(r), _p(k), _p(v), stride, _p(log_decay), _p(u), _p(state), state.stride(0), _p(y),
+              _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"))
+    if plan is None:
+        _call("lily_wkv_scan", *common, requests, heads, d, _dt(r), 0, None, None, None, None, None, _stream())
+        return y
+    need = wkv_workspace_floats(plan, heads, d)
+    if workspace is None or workspace.dtype != torch.float32 or workspace.numel() < need:
+        raise KernelError(f"wkv_scan: chunks need a float32 workspace of {need}")
+    ws_state = workspace
+    ws_decay = workspace[plan.items * heads * d * d:]
+    chunks = (_p(plan.item_req), _p(plan.item_start), _p(plan.item_len), _p(ws_state), _p(ws_decay))
+    _call("lily_wkv_scan", *common, plan.items, heads, d, _dt(r), 1, *chunks, _stream())
+    _call("lily_wkv_combine", _p(state), state.stride(0), _i32(slots, "slots"), _p(ws_state), _p(ws_decay), _p(plan.long_req),
+          _p(plan.long_first), _p(plan.long_count), plan.longs, heads, d, _stream())
+    _call("lily_wkv_scan", *common, plan.items, heads, d, _dt(r), 2, *chunks, _stream())
+    if plan.shorts:
+        # the short portions of the same step run whole, from and to their slots
+        _call("lily_wkv_scan", *common, plan.shorts, heads, d, _dt(r), 3, _p(plan.short_reqs), None, None, None, None, _stream())
     return y
 
 
@@ -1167,6 +1238,16 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, t
                          max_tiles, top)
 
 
+_OWN_GROUPED = os.environ.get("LILY_B200_GROUPED_GEMM", "") == "own"
+
+
+def grouped_library_takes(dtype: torch.dtype, width: int, ff: int) -> bool:
+    """Whether the experts' two products go to the library's grouped product (bfloat16 with rows of whole 16-byte
+    units); everything else, and float32 always, runs on this package's grouped kernel."""
+    return (dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0 and hasattr(torch, "_grouped_mm")
+            and not _OWN_GROUPED)
+
+
 def moe_experts(h: torch.Tensor, routing: ExpertRouting, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float,
                 alpha: float) -> torch.Tensor:
     """The chosen experts' outputs summed with their weights, float32 [tokens, width].  ``w_gate_up`` [experts, 2 ff,
@@ -1179,6 +1260,18 @@ def moe_experts(h: torch.Tensor, routing: ExpertRouting, w_gate_up: torch.Tensor
     pairs = tokens * r.top
     experts = w_down.shape[0] if w_down.dim() == 3 else 0
     ff = w_down.shape[2] if experts else 0
+    if experts and grouped_library_takes(h.dtype, width, ff):
+        # bfloat16: the library's grouped product over the rows in grouped order (groups end at offsets[1:])
+        ends = r.offsets[1:]
+        rows = torch.empty((pairs, width), dtype=h.dtype, device=h.device)
+        _call("lily_moe_gather", _p(h), width, _p(r.offsets), experts, _p(r.order), r.top, pairs, _p(rows), _dt(h), _stream())
+        gate_up = torch._grouped_mm(rows, w_gate_up.transpose(1, 2), offs=ends)
+        act = torch.empty((pairs, ff), dtype=h.dtype, device=h.device)
+        _call("lily_moe_activation", _p(gate_up), ff, pairs, _p(act), float(limit), float(alpha), _dt(h), _stream())
+        y = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)
+        out = torch.empty((tokens, width), dtype=torch.float32, device=h.device)
+        _call("lily_moe_combine_rows", _p(y), _p(h), _p(r.place), _p(r.weights), tokens, r.top, width, _p(out), _dt(h), _stream())
+        return out
     y = torch.empty((max(pairs, 1), width), dtype=torch.float32, device=h.device)
     if experts:
         if w_gate_up.dtype != h.dtype or w_down.dtype != h.dtype or tuple(w_gate_up.shape) != (experts, 2 * ff, width):

@@ -75,7 +75,10 @@ template <typename T>
 __global__ void wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
                                 const float* __restrict__ lw, const float* __restrict__ u, float* __restrict__ state,
                                 size_t state_stride, float* __restrict__ y, const int* __restrict__ cu_seqlens,
-                                const int* __restrict__ slots, int heads, int d, int ks) {
+                                const int* __restrict__ slots, int heads, int d, int ks, int mode,
+                                const int* __restrict__ item_req, const int* __restrict__ item_start,
+                                const int* __restrict__ item_len, float* __restrict__ ws_state,
+                                float* __restrict__ ws_decay) {
     extern __shared__ __align__(16) float sm[];
     const int rows = ks * (WKV_NPT + WKV_PAD);              // floats of one token's r (or k, or decay) in shared memory
     float* rs = sm;                                          // [TT][rows]
@@ -85,21 +88,34 @@ __global__ void wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k
     float* bonus = vs + WKV_TT * d;                          // [TT]: sum_i r[i] u[i] k[i]
     float* us = bonus + WKV_TT;                              // [d]
     pdl_enter_small();
-    const int head = blockIdx.x, req = blockIdx.y;
-    const int tok0 = cu_seqlens[req], n = cu_seqlens[req + 1] - tok0;
+    // mode 0: blockIdx.y is a request; all its new tokens, from and to the matrices in its slot.
+    // modes 1 and 2: blockIdx.y is an item (a chunk of a long portion).  1: from zero, no outputs; leaves the chunk's own
+    // matrices and the product of its decays in the workspace.  2: from the matrices the workspace holds for the
+    // chunk's start (wkv_combine put them there), writes the outputs and no state.
+    const int head = blockIdx.x, item = blockIdx.y;
+    // mode 3: as mode 0 for the requests the list names (the short portions of a step that also has long ones).
+    const bool whole = mode == 0 || mode == 3;
+    const int req = mode == 0 ? item : item_req[item];
+    const int tok0 = cu_seqlens[req] + (whole ? 0 : item_start[item]);
+    const int n = whole ? cu_seqlens[req + 1] - tok0 : item_len[item];
     if (n <= 0) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
     const int part = tid % ks, col0 = (blockIdx.z * (blockDim.x / ks) + tid / ks) * WKV_PC;  // this thread's key rows and value columns
     const bool live = col0 < d;
     const int hd = heads * d;
-    float* st = state + (size_t)slots[req] * state_stride + (size_t)head * d * d;
+    float* st = whole ? state + (size_t)slots[req] * state_stride + (size_t)head * d * d
+                          : ws_state + ((size_t)item * heads + head) * d * d;
     float S[WKV_NPT][WKV_PC];
+    float wprod[WKV_NPT];                                   // mode 1, first column group: the product of the rows' decays
+#pragma unroll
+    for (int i = 0; i < WKV_NPT; ++i) wprod[i] = 1.f;
+    const bool keeps_decay = mode == 1 && blockIdx.z == 0 && tid / ks == 0;
 #pragma unroll
     for (int i = 0; i < WKV_NPT; ++i) {
         const int row = part * WKV_NPT + i;
 #pragma unroll
         for (int c = 0; c < WKV_PC; ++c)
-            S[i][c] = (live && row < d && col0 + c < d) ? st[(size_t)row * d + col0 + c] : 0.f;
+            S[i][c] = (mode != 1 && live && row < d && col0 + c < d) ? st[(size_t)row * d + col0 + c] : 0.f;
     }
     for (int i = tid; i < d; i += blockDim.x) us[i] = u[(size_t)head * d + i];
     // rows beyond d read zeros for r and k, so the padded entries of S stay zero and add nothing
@@ -157,7 +173,11 @@ __global__ void wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k
             for (int c = 0; c < WKV_PC; ++c) {
                 for (int o = 1; o < ks; o <<= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
             }
-            if (live && part == 0) {
+            if (keeps_decay) {
+#pragma unroll
+                for (int i = 0; i < WKV_NPT; ++i) wprod[i] *= wp[i];
+            }
+            if (mode != 1 && live && part == 0) {
                 const float bt = bonus[t];
                 float* dst = y + (size_t)(tok0 + t0 + t) * hd + (size_t)head * d + col0;
 #pragma unroll
@@ -166,7 +186,7 @@ __global__ void wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k
             }
         }
     }
-    if (live) {
+    if (live && mode != 2) {
 #pragma unroll
         for (int i = 0; i < WKV_NPT; ++i) {
             const int row = part * WKV_NPT + i;
@@ -175,6 +195,37 @@ __global__ void wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k
                 if (row < d && col0 + c < d) st[(size_t)row * d + col0 + c] = S[i][c];
         }
     }
+    if (keeps_decay) {
+#pragma unroll
+        for (int i = 0; i < WKV_NPT; ++i) {
+            const int row = part * WKV_NPT + i;
+            if (row < d) ws_decay[((size_t)item * heads + head) * d + row] = wprod[i];
+        }
+    }
+}
+
+// Walks the chunks of each long portion in order: S <- diag(decay_c) S + state_c, leaving in the workspace the
+// matrices each chunk starts from and in the slot the last ones.  grid (ceil(heads * d * d / 256), long portions).
+__global__ void wkv_combine_kernel(float* __restrict__ state, size_t state_stride, const int* __restrict__ slots,
+                                   float* __restrict__ ws_state, const float* __restrict__ ws_decay,
+                                   const int* __restrict__ long_req, const int* __restrict__ long_first,
+                                   const int* __restrict__ long_count, int heads, int d) {
+    pdl_wait();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;               // (head, row, column)
+    const int per = heads * d * d;
+    if (e >= per) return;
+    const int k = blockIdx.y;
+    const int head = e / (d * d), row = (e / d) % d;
+    float* st = state + (size_t)slots[long_req[k]] * state_stride + e;
+    float S = *st;
+    const int first = long_first[k], count = long_count[k];
+    for (int c = 0; c < count; ++c) {
+        float* own = ws_state + (size_t)(first + c) * per + e;
+        const float local = *own;
+        *own = S;
+        S = fmaf(ws_decay[((size_t)(first + c) * heads + head) * d + row], S, local);
+    }
+    *st = S;
 }
 
 
@@ -240,8 +291,13 @@ LILY_API int lily_wkv_max_head_dim() { return 256; }
 
 LILY_API int lily_wkv_scan(const void* r, const void* k, const void* v, int in_stride, const float* lw, const float* u,
                            float* state, size_t state_stride, float* y, const int* cu_seqlens, const int* slots,
-                           int requests, int heads, int d, int dtype, cudaStream_t stream) {
+                           int requests, int heads, int d, int dtype, int mode, const int* item_req, const int* item_start,
+                           const int* item_len, float* ws_state, float* ws_decay, cudaStream_t stream) {
+    // requests: the grid's second axis (requests in mode 0, items in modes 1 and 2)
     if (requests == 0) return 0;
+    LILY_REQUIRE(mode >= 0 && mode <= 3, "wkv_scan: mode %d", mode);
+    LILY_REQUIRE(mode == 0 || item_req, "wkv_scan: a list of requests is needed");
+    LILY_REQUIRE(mode == 0 || mode == 3 || (item_start && item_len && ws_state && ws_decay), "wkv_scan: chunks need their lists and a workspace");
     LILY_REQUIRE(heads > 0 && d > 0 && d <= 256, "wkv_scan: %d heads of size %d (sizes up to 256)", heads, d);
     LILY_REQUIRE(requests <= 65535, "wkv_scan: %d heads, %d requests", heads, requests);
     int ks = 1;
@@ -261,7 +317,8 @@ LILY_API int lily_wkv_scan(const void* r, const void* k, const void* v, int in_s
             granted = smem;                                                                                           \
         }                                                                                                             \
         launch_pdl(wkv_scan_kernel<T>, grid, block, smem, stream, (const T*)r, (const T*)k, (const T*)v, in_stride, lw, u, \
-                   state, state_stride, y, cu_seqlens, slots, heads, d, ks);                                          \
+                   state, state_stride, y, cu_seqlens, slots, heads, d, ks, mode, item_req, item_start, item_len, ws_state, \
+                   ws_decay);                                                                                         \
     } while (0)
     if (dtype == kBF16) GO(__nv_bfloat16); else GO(float);
 #undef GO
@@ -282,5 +339,16 @@ LILY_API int lily_group_rmsnorm_gate(const float* y, const void* g, int g_stride
         launch_pdl(group_rmsnorm_gate_kernel<float>, grid, block, 0, stream, y, (const float*)g, g_stride, gain, (float*)out,
                    inner, inner / groups, groups, eps);
     LILY_CHECK_LAUNCH("group_rmsnorm_gate");
+    return 0;
+}
+
+LILY_API int lily_wkv_combine(float* state, size_t state_stride, const int* slots, float* ws_state, const float* ws_decay,
+                              const int* long_req, const int* long_first, const int* long_count, int longs, int heads, int d,
+                              cudaStream_t stream) {
+    if (longs == 0) return 0;
+    const int per = heads * d * d;
+    launch_pdl(wkv_combine_kernel, dim3((per + 255) / 256, longs), dim3(256), 0, stream, state, state_stride, slots, ws_state,
+               ws_decay, long_req, long_first, long_count, heads, d);
+    LILY_CHECK_LAUNCH("wkv_combine");
     return 0;
 }

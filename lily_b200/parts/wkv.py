@@ -111,7 +111,13 @@ class Wkv(Mixer):
         gate = ops.linear(mixes[3], self.w_g)
         low = ops.linear(mixes[4], self.w_1, out_dtype=torch.float32)            # [tokens, rank], float32 from here on
         log_decay = ops.wkv_decay(low, self.w_2t, self.w_0)
+        # long portions run as chunks side by side; the cut is planned once a step for all layers
+        plan = batch.plan(("wkv_plan",), lambda b: ops.wkv_plan(b.h_new_lens, b.token_ids.device))
+        need = ops.wkv_workspace_floats(plan, s.heads, s.head_dim)
+        room = batch.workspace.floats("wkv_chunks", need) if need and batch.workspace is not None else None
+        if need and room is None:
+            plan = None                                    # no scratch to be had: every portion runs whole
         y = ops.wkv_scan(r, k, v, log_decay, self.u, state, batch.cu_seqlens, batch.slots, batch.num_requests, s.heads,
-                         s.head_dim)
+                         s.head_dim, plan=plan, workspace=room)
         normed = ops.group_rmsnorm_gate(y, gate, self.gain, s.heads, s.norm_eps)
         return ops.linear_auto(normed, self.w_o)

@@ -473,7 +473,15 @@ def wkv_max_head_dim():
     return 256
 
 
-def wkv_scan(r, k, v, log_decay, u, state, cu_seqlens, slots, requests, heads, d):
+def wkv_plan(new_lens, device):
+    return None
+
+
+def wkv_workspace_floats(plan, heads, d):
+    return 0
+
+
+def wkv_scan(r, k, v, log_decay, u, state, cu_seqlens, slots, requests, heads, d, plan=None, workspace=None):
     y = torch.empty((r.shape[0], heads * d), dtype=torch.float32, device=r.device)
     for q in range(requests):
         t0, t1 = int(cu_seqlens[q]), int(cu_seqlens[q + 1])

@@ -121,6 +121,46 @@ def test_recurrence_against_the_plain_loop(device, heads, d):
             assert float((state - want_state.float()).abs().max()) < 2e-5 * max(1.0, float(want_state.abs().max()))
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,d", [(2, 64), (3, 24)])
+def test_recurrence_in_chunks_side_by_side(heads, d):
+    """Long portions run as chunks side by side (each first from zero, then from the matrices it starts from), beside
+    short portions of the same step that run whole; two steps, so the second continues from the slots."""
+    from lily_b200.csrc import ops
+    device = "cuda"
+    g = torch.Generator().manual_seed(d)
+    lens = [[700, 40, 300], [257, 1, 520]]                       # per step: new tokens of three requests
+    total = [sum(step[q] for step in lens) for q in range(3)]
+    seqs = []
+    for n in total:
+        r, k, v = (torch.randn(n, heads, d, generator=g) for _ in range(3))
+        seqs.append((r, k / math.sqrt(d), v, -torch.exp(torch.rand(n, heads, d, generator=g) * 6 - 6)))
+    u = torch.randn(heads, d, generator=g)
+    state = torch.zeros(5, heads * d * d + 3, device=device)
+    slots = i32([3, 1, 4], device)
+    got = [[], [], []]
+    done = [0, 0, 0]
+    for step in lens:
+        cat = lambda j: torch.cat([seqs[q][j][done[q]:done[q] + step[q]] for q in range(3)]).reshape(sum(step), heads * d).to(device)
+        cu = i32([0, step[0], step[0] + step[1], sum(step)], device)
+        plan = ops.wkv_plan(step, device)
+        assert plan is not None and plan.longs == 2 and plan.shorts == 1
+        room = torch.empty(ops.wkv_workspace_floats(plan, heads, d), device=device)
+        y = ops.wkv_scan(cat(0), cat(1), cat(2), cat(3), u.to(device), state, cu, slots, 3, heads, d, plan=plan, workspace=room).cpu()
+        at = 0
+        for q in range(3):
+            got[q].append(y[at:at + step[q]])
+            at += step[q]
+            done[q] += step[q]
+    for q in range(3):
+        r, k, v, lw = seqs[q]
+        want, want_state = pg.wkv_recurrence(r.double(), k.double(), v.double(), torch.exp(lw.double()), u.double())
+        out = torch.cat(got[q]).view(-1, heads, d)
+        assert float((out - want.float()).abs().max()) < 3e-5 * float(want.abs().max()), q
+        kept = state[int(slots[q]), :heads * d * d].view(heads, d, d).cpu()
+        assert float((kept - want_state.float()).abs().max()) < 3e-5 * max(1.0, float(want_state.abs().max()))
+
+
 @pytest.mark.parametrize("device", DEVICES)
 def test_recurrence_remembers_the_first_token(device):
     """With decays next to one, a value written by the first token is read 400 tokens later, through 399 decoded
