@@ -142,7 +142,7 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
         table = (torch.randperm(pages, device=dev, generator=g) + 1).view(1, pages).to(torch.int32)
         q = (rnd(tokens, h_ * row) / 8).to(dt)
         out = torch.empty((tokens, h_ * rank), device=dev, dtype=dt)
-        tile = ops.prefill_tile_rows(dt, row, page, tokens, dv=rank, values_in_keys=True)
+        tile = ops.prefill_tile_rows(dt, row, page, tokens, dv=rank, values_in_keys=True, heads=h_)
         tr, ts = ops.prefill_tiles([0], [tokens], 0, tile, dev)
         fns.append(lambda q=q, cache=cache, table=table, out=out, tr=tr, ts=ts, tile=tile: ops.attention_prefill(
             q, cache, table, cu1, pre, tr, ts, out, h_, 1, row, page, la["scale"], window, tile_rows=tile, dv=rank, values_in_keys=True))

@@ -50,6 +50,8 @@ _SIGNATURES = {
                       _i, _vp, _vp, _i, _vp],
     "lily_ssd_combine": [_vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "lily_gated_group_rmsnorm": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+    "lily_latent_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "lily_latent_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
     "lily_add_rmsnorm_multi": [_vp, _vp, _i, _i, _sz, _vp, _i, _i, _sz, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _vp],
     "lily_gemm_fp32_heads": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _sz, _sz, _vp],
     "lily_token_shift_mix": [_vp, _i, _i, _vp, _i, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _i, _vp],
@@ -109,6 +111,10 @@ def library():
         lib.lily_attention_decode_scratch_floats.restype = _sz
         lib.lily_normed_mean_max.restype = _i
         lib.lily_wkv_max_head_dim.restype = _i
+        lib.lily_latent_attention_mma_takes.argtypes = [_i, _i]
+        lib.lily_latent_attention_mma_takes.restype = _i
+        lib.lily_latent_attention_mma_tile_tokens.argtypes = [_i]
+        lib.lily_latent_attention_mma_tile_tokens.restype = _i
         lib.lily_moe_tile_rows.restype = _i
         _lib = lib
     return _lib
@@ -533,11 +539,24 @@ def uses_tcgen05_attention(dtype: torch.dtype, d: int, page_size: int, new_token
             and bool(library().lily_attention_prefill_tc_takes(int(d), int(page_size))))
 
 
+_SIMT_LATENT = os.environ.get("LILY_B200_LATENT_ATTENTION", "") == "simt"
+
+
+def latent_tensor_cores(dtype: torch.dtype, d: int, dv: Optional[int], nkv: int = 1, softcap: Optional[float] = None) -> bool:
+    """Whether attention whose values are columns of the key rows runs on the tensor-core kernel for cached latents
+    (bfloat16, one shared row a position, rows of whole 16-byte pieces, an even value width of up to 512, plain scores)."""
+    return (dtype == torch.bfloat16 and nkv == 1 and not softcap and dv is not None and not _SIMT_LATENT
+            and bool(library().lily_latent_attention_mma_takes(int(d), int(dv))))
+
+
 def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size: int = 0, new_tokens: int = 0,
-                      softcap: Optional[float] = None, dv: Optional[int] = None, values_in_keys: bool = False) -> int:
+                      softcap: Optional[float] = None, dv: Optional[int] = None, values_in_keys: bool = False,
+                      heads: int = 0) -> int:
     """New tokens per tile of the prefill kernel that will take this precision, head size (``dv`` for the values
     where it differs), page size, number of new tokens and kind of scores."""
     lib = library()
+    if values_in_keys and heads and latent_tensor_cores(dtype, d, dv, softcap=softcap):
+        return int(lib.lily_latent_attention_mma_tile_tokens(int(heads)))
     same = (dv is None or dv == d) and not values_in_keys
     if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens):
         return int(lib.lily_attention_prefill_tc_rows())
@@ -571,6 +590,13 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
     lib = library()
     dv = int(dv or d)
     cap = float(softcap or 0.0)
+    if (values_in_keys and latent_tensor_cores(q.dtype, d, dv, nkv, softcap)
+            and tile_rows == int(lib.lily_latent_attention_mma_tile_tokens(int(nq)))):
+        _call("lily_latent_attention_prefill_mma", _p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"),
+              block_table.shape[-1], _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"),
+              _i32(tile_req, "tile_req"), _i32(tile_start, "tile_start"), tile_req.numel(), int(tile_rows), nq, d, dv,
+              page_size, int(window or 0), float(scale), _stream())
+        return
     tensor_cores = dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d)
     base_rows = int(lib.lily_attention_prefill_mma_rows() if tensor_cores else lib.lily_attention_prefill_simt_rows())
     if tile_rows is not None and tile_rows != base_rows:
@@ -616,7 +642,13 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
               _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, nkv, d, page_size, int(window or 0),
               float(scale))
-    if dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d):
+    if values_in_keys and latent_tensor_cores(q.dtype, d, dv, nkv, softcap) and not stages:
+        _call("lily_latent_attention_decode_mma", _p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"),
+              block_table.shape[-1], _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits, nq, d, dv, page_size,
+              int(window or 0), float(scale), _stream())
+        if splits > 1:
+            _call("lily_attention_combine", _p(scratch), _p(out), requests, nq, dv, splits, _dt(q), _stream())
+    elif dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d):
         _call("lily_attention_decode_mma", *common, int(stages), cap, _stream())   # merges the splits itself (cluster, or combine behind)
         if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
             launches["count"] += 1                                   # the combine kernel, launched inside

@@ -121,7 +121,8 @@ class LatentAttention(Mixer):
                                                dv=s.kv_rank, values_in_keys=True)
             rows = tiles = None
             if b.num_requests > nd:
-                rows = ops.prefill_tile_rows(dtype, s.row, page, b.num_tokens - nd, dv=s.kv_rank, values_in_keys=True)
+                rows = ops.prefill_tile_rows(dtype, s.row, page, b.num_tokens - nd, dv=s.kv_rank, values_in_keys=True,
+                                             heads=s.num_heads)
                 tiles = ops.prefill_tiles(b.h_prefix_lens, b.h_new_lens, nd, rows, b.token_ids.device)
             return AttentionPlan(decode, rows, tiles)
         return batch.plan(key, make)

@@ -209,7 +209,7 @@ def uses_tensor_cores(dtype, d):
     return dtype == torch.bfloat16 and d in (64, 128, 192, 256)
 
 
-def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0, softcap=None, dv=None, values_in_keys=False):
+def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0, softcap=None, dv=None, values_in_keys=False, heads=0):
     return 32
 
 

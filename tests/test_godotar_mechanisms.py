@@ -246,7 +246,7 @@ def run_latent(ops, device, dtype, h, w, c, eps, page, cuts):
             ops.attention_decode(queries, cache, table, i32([done + 1], device), mixed, scratch, plan.splits, heads, 1, row,
                                  page, float(c["scale"]), window, dv=rank, values_in_keys=True)
         else:
-            tile = ops.prefill_tile_rows(dtype, row, page, n, dv=rank, values_in_keys=True)
+            tile = ops.prefill_tile_rows(dtype, row, page, n, dv=rank, values_in_keys=True, heads=heads)
             tr, ts = ops.prefill_tiles([done], [n], 0, tile, device)
             ops.attention_prefill(queries, cache, table, i32([0, n], device), i32([done], device), tr, ts, mixed, heads, 1,
                                   row, page, float(c["scale"]), window, tile_rows=tile, dv=rank, values_in_keys=True)
@@ -260,7 +260,7 @@ def run_latent(ops, device, dtype, h, w, c, eps, page, cuts):
 
 @pytest.mark.parametrize("device", DEVICES)
 @pytest.mark.parametrize("heads,d,rot,dv,q_rank,rank", [(3, 8, 4, 12, 20, 24), (2, 32, 16, 32, 48, 128), (1, 16, 2, 5, 9, 33),
-                                                        (5, 12, 32, 8, 16, 72)])
+                                                        (5, 12, 32, 8, 16, 72), (40, 16, 64, 16, 32, 512), (16, 8, 8, 8, 24, 264)])
 @pytest.mark.parametrize("window", [37, None, 64])
 def test_one_position_that_stands_out(device, heads, d, rot, dv, q_rank, rank, window):
     """The inputs at three positions (at a page border and far back) are made so that their cached latent scores high
@@ -288,6 +288,44 @@ def test_one_position_that_stands_out(device, heads, d, rot, dv, q_rank, rank, w
             got = run_latent(ops, device, dtype, h, w, c, eps, page, cuts)
             tol = 5e-5 if dtype == torch.float32 else 6e-2
             assert float((got - want).abs().max()) < tol * max(1.0, float(want.abs().max())), (dtype, cuts[:3])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,row,rank", [(4, 144, 128), (16, 576, 512), (33, 72, 40), (3, 28, 24)])
+@pytest.mark.parametrize("window", [None, 100])
+def test_latent_decode_in_key_ranges(heads, row, rank, window):
+    """One new token a request over cached rows of unequal lengths, the keys cut into 1 to 7 ranges that are merged
+    afterwards (tensor cores where the sizes allow, CUDA cores else): against a plain softmax over the same rows."""
+    from lily_b200.csrc import ops
+    device, page, scale = "cuda", 16, 0.2
+    g = torch.Generator().manual_seed(row)
+    lens = [1, 37, 300, 64, 129]
+    pages = [-(-n // page) for n in lens]
+    width = max(pages)
+    order = (torch.randperm(sum(pages), generator=g) + 1).tolist()
+    table = torch.zeros(len(lens), width, dtype=torch.int32)
+    at = 0
+    for r, n in enumerate(pages):
+        table[r, :n] = torch.tensor(order[at:at + n], dtype=torch.int32)
+        at += n
+    for dtype in (torch.float32, torch.bfloat16):
+        cache = (torch.randn(sum(pages) + 1, page * row, generator=g) * 0.7).to(device=device, dtype=dtype)
+        q = torch.randn(len(lens), heads * row, generator=g).to(device=device, dtype=dtype)
+        rows = cache.view(-1, page, row).float()
+        want = torch.empty(len(lens), heads, rank)
+        for r, n in enumerate(lens):
+            keys = torch.stack([rows[int(table[r, j // page]), j % page] for j in range(n)]).cpu()
+            sc = (q[r].float().cpu().view(heads, row) @ keys.t()) * scale
+            if window:
+                sc[:, :max(0, n - window)] = float("-inf")
+            want[r] = torch.softmax(sc, -1) @ keys[:, :rank]
+        for splits in (1, 2, 7):
+            out = torch.empty(len(lens), heads * rank, device=device, dtype=dtype)
+            scratch = torch.empty(max(1, ops.decode_scratch_floats(len(lens), heads, rank, splits)), device=device)
+            ops.attention_decode(q, cache, table.to(device), i32(lens, device), out, scratch, splits, heads, 1, row, page, scale,
+                                 window, dv=rank, values_in_keys=True)
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            assert float((out.float().cpu().view(len(lens), heads, rank) - want).abs().max()) < tol * float(want.abs().max()), (dtype, splits)
 
 
 @pytest.mark.parametrize("device", DEVICES)
