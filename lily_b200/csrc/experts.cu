@@ -27,13 +27,37 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int width, const float
                                  float* __restrict__ weights) {
     __shared__ float s[ROUTE_MAX];
     __shared__ float picked[ROUTE_TOP_MAX];
+    extern __shared__ __align__(16) float xs[];              // [width]: the token's row
     pdl_enter_small();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const T* x = h + (size_t)t * width;
+    // the token's row once into shared memory as float32; then every warp's outputs read it from there, eight columns
+    // a lane and turn with all their loads asked for ahead of the sums (a plain loop waits for memory at every step)
+    for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_float(x[c]);
+    __syncthreads();
     for (int e = warp; e < outputs; e += nwarp) {
         const float* w = router + (size_t)e * width;
         float z = 0.f;
-        for (int c = lane; c < width; c += 32) z = fmaf(to_float(x[c]), w[c], z);
+        int c = lane * 4;
+        if ((width & 3) == 0) {
+            float4 wv[4], xv[4];
+            for (; c + 3 * 128 < width; c += 4 * 128) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    wv[u] = *reinterpret_cast<const float4*>(w + c + u * 128);
+                    xv[u] = *reinterpret_cast<const float4*>(xs + c + u * 128);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    z = fmaf(xv[u].x, wv[u].x, fmaf(xv[u].y, wv[u].y, fmaf(xv[u].z, wv[u].z, fmaf(xv[u].w, wv[u].w, z))));
+            }
+            for (; c < width; c += 128) {
+                const float4 wq = *reinterpret_cast<const float4*>(w + c), xq = *reinterpret_cast<const float4*>(xs + c);
+                z = fmaf(xq.x, wq.x, fmaf(xq.y, wq.y, fmaf(xq.z, wq.z, fmaf(xq.w, wq.w, z))));
+            }
+        } else {
+            for (c = lane; c < width; c += 32) z = fmaf(xs[c], w[c], z);
+        }
         z = warp_sum(z);
         if (lane == 0) s[e] = z;
     }
@@ -279,11 +303,12 @@ LILY_API int lily_moe_route(const void* h, int tokens, int width, const float* r
     if (tokens == 0) return 0;
     LILY_REQUIRE(outputs >= 1 && outputs <= ROUTE_MAX, "moe_route: %d router outputs (up to %d)", outputs, ROUTE_MAX);
     LILY_REQUIRE(top >= 1 && top <= outputs && top <= ROUTE_TOP_MAX, "moe_route: top %d of %d", top, outputs);
+    LILY_REQUIRE(width > 0 && width <= 10240, "moe_route: rows of %d numbers (up to 10240)", width);
     if (dtype == kBF16)
-        launch_pdl(moe_route_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, (const __nv_bfloat16*)h, width, router,
+        launch_pdl(moe_route_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), (size_t)width * sizeof(float), stream, (const __nv_bfloat16*)h, width, router,
                    correction, outputs, top, chosen, weights);
     else
-        launch_pdl(moe_route_kernel<float>, dim3(tokens), dim3(128), 0, stream, (const float*)h, width, router, correction,
+        launch_pdl(moe_route_kernel<float>, dim3(tokens), dim3(128), (size_t)width * sizeof(float), stream, (const float*)h, width, router, correction,
                    outputs, top, chosen, weights);
     LILY_CHECK_LAUNCH("moe_route");
     return 0;

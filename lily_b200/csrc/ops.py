@@ -1069,8 +1069,8 @@ def wkv_max_head_dim() -> int:
     return int(library().lily_wkv_max_head_dim())
 
 
-WKV_CHUNK = 128         # tokens a chunk of a long portion
-WKV_DIRECT = 256        # portions up to this many tokens run in one piece, from and to the matrices in the slot
+WKV_CHUNK = 64          # tokens a chunk of a long portion
+WKV_DIRECT = 128        # portions up to this many tokens run in one piece, from and to the matrices in the slot
 
 
 @dataclass

@@ -46,20 +46,32 @@ __global__ void token_shift_mix_kernel(const T* __restrict__ h, int tokens, int 
 
 // ---------------------------------------------------------------------------- the decay's logarithm
 
-// grid (tokens, ceil(cols / 128)), block 128; a [tokens, rank] float32, w2t [rank, cols] float32 (the second
-// matrix of the low-rank pair, transposed so that neighbouring threads read neighbouring numbers), w0 [cols].
-__global__ void wkv_decay_kernel(const float* __restrict__ a, int rank, const float* __restrict__ w2t,
+// grid (ceil(tokens / 8), ceil(cols / 128)), block 128; a [tokens, rank] float32, w2t [rank, cols] float32 (the second
+// matrix of the low-rank pair, transposed so that neighbouring threads read neighbouring numbers), w0 [cols].  A block
+// takes eight tokens, so a number of w2t read once serves eight sums.
+constexpr int DECAY_TOKENS = 8;
+__global__ void wkv_decay_kernel(const float* __restrict__ a, int tokens, int rank, const float* __restrict__ w2t,
                                  const float* __restrict__ w0, int cols, float* __restrict__ lw) {
-    extern __shared__ float th[];          // tanh(a[t, :])
+    extern __shared__ float th[];          // [8][rank]: tanh(a[t, :])
     pdl_enter_small();
-    const int t = blockIdx.x;
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(a[(size_t)t * rank + j]);
+    const int t0 = blockIdx.x * DECAY_TOKENS, nt = min(DECAY_TOKENS, tokens - t0);
+    for (int i = threadIdx.x; i < DECAY_TOKENS * rank; i += blockDim.x)
+        th[i] = i < nt * rank ? tanhf(a[(size_t)t0 * rank + i]) : 0.f;
     __syncthreads();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= cols) return;
-    float z = 0.f;
-    for (int j = 0; j < rank; ++j) z = fmaf(th[j], w2t[(size_t)j * cols + c], z);
-    lw[(size_t)t * cols + c] = -expf(z + w0[c]);
+    float z[DECAY_TOKENS];
+#pragma unroll
+    for (int t = 0; t < DECAY_TOKENS; ++t) z[t] = 0.f;
+    for (int j = 0; j < rank; ++j) {
+        const float w = w2t[(size_t)j * cols + c];
+#pragma unroll
+        for (int t = 0; t < DECAY_TOKENS; ++t) z[t] = fmaf(th[t * rank + j], w, z[t]);
+    }
+    const float b = w0[c];
+#pragma unroll
+    for (int t = 0; t < DECAY_TOKENS; ++t)
+        if (t < nt) lw[(size_t)(t0 + t) * cols + c] = -expf(z[t] + b);
 }
 
 // ---------------------------------------------------------------------------- the recurrence
@@ -69,7 +81,7 @@ __global__ void wkv_decay_kernel(const float* __restrict__ a, int rank, const fl
 // PC neighbouring value columns of the head's matrix and hold NPT of its key rows each in registers (rows
 // lane * NPT ... of a padded count ks * NPT >= d), so that one r, k and decay read from shared memory serve 2 * PC
 // multiply-adds.  The tokens of the request run one after another, staged TT at a time in shared memory.
-constexpr int WKV_NPT = 16, WKV_PC = 4, WKV_TT = 16, WKV_PAD = 4;
+constexpr int WKV_NPT = 8, WKV_PC = 4, WKV_TT = 16, WKV_PAD = 4;
 
 template <typename T>
 __global__ void wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
@@ -164,14 +176,16 @@ __global__ void wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k
                 for (int e = 0; e < 4; ++e) {
 #pragma unroll
                     for (int c = 0; c < WKV_PC; ++c) {
-                        acc[c] = fmaf(rr[e], S[i + e][c], acc[c]);
+                        if (mode != 1) acc[c] = fmaf(rr[e], S[i + e][c], acc[c]);
                         S[i + e][c] = fmaf(wq[e], S[i + e][c], kq[e] * vv[c]);
                     }
                 }
             }
+            if (mode != 1) {
 #pragma unroll
-            for (int c = 0; c < WKV_PC; ++c) {
-                for (int o = 1; o < ks; o <<= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+                for (int c = 0; c < WKV_PC; ++c) {
+                    for (int o = 1; o < ks; o <<= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+                }
             }
             if (keeps_decay) {
 #pragma unroll
@@ -219,11 +233,21 @@ __global__ void wkv_combine_kernel(float* __restrict__ state, size_t state_strid
     float* st = state + (size_t)slots[long_req[k]] * state_stride + e;
     float S = *st;
     const int first = long_first[k], count = long_count[k];
-    for (int c = 0; c < count; ++c) {
-        float* own = ws_state + (size_t)(first + c) * per + e;
-        const float local = *own;
-        *own = S;
-        S = fmaf(ws_decay[((size_t)(first + c) * heads + head) * d + row], S, local);
+    for (int c0 = 0; c0 < count; c0 += 4) {                             // four chunks' numbers asked for before the first is used
+        float local[4], decay[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const bool in = c0 + j < count;
+            local[j] = in ? ws_state[(size_t)(first + c0 + j) * per + e] : 0.f;
+            decay[j] = in ? ws_decay[((size_t)(first + c0 + j) * heads + head) * d + row] : 1.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (c0 + j < count) {
+                ws_state[(size_t)(first + c0 + j) * per + e] = S;
+                S = fmaf(decay[j], S, local[j]);
+            }
+        }
     }
     *st = S;
 }
@@ -279,10 +303,10 @@ LILY_API int lily_token_shift_mix(const void* h, int tokens, int width, const fl
 LILY_API int lily_wkv_decay(const float* a, int tokens, int rank, const float* w2t, const float* w0, int cols, float* lw,
                             cudaStream_t stream) {
     if (tokens == 0) return 0;
-    LILY_REQUIRE(rank > 0 && cols > 0 && rank <= 8192, "wkv_decay: rank=%d cols=%d", rank, cols);
-    dim3 grid(tokens, (cols + 127) / 128), block(128);
-    LILY_REQUIRE(grid.y <= 65535, "wkv_decay: %d columns", cols);
-    launch_pdl(wkv_decay_kernel, grid, block, (size_t)rank * sizeof(float), stream, a, rank, w2t, w0, cols, lw);
+    LILY_REQUIRE(rank > 0 && cols > 0, "wkv_decay: rank=%d cols=%d", rank, cols);
+    dim3 grid((tokens + DECAY_TOKENS - 1) / DECAY_TOKENS, (cols + 127) / 128), block(128);
+    LILY_REQUIRE(grid.y <= 65535 && rank <= 1024, "wkv_decay: %d columns, rank %d", cols, rank);
+    launch_pdl(wkv_decay_kernel, grid, block, (size_t)DECAY_TOKENS * rank * sizeof(float), stream, a, tokens, rank, w2t, w0, cols, lw);
     LILY_CHECK_LAUNCH("wkv_decay");
     return 0;
 }
@@ -298,7 +322,7 @@ LILY_API int lily_wkv_scan(const void* r, const void* k, const void* v, int in_s
     LILY_REQUIRE(mode >= 0 && mode <= 3, "wkv_scan: mode %d", mode);
     LILY_REQUIRE(mode == 0 || item_req, "wkv_scan: a list of requests is needed");
     LILY_REQUIRE(mode == 0 || mode == 3 || (item_start && item_len && ws_state && ws_decay), "wkv_scan: chunks need their lists and a workspace");
-    LILY_REQUIRE(heads > 0 && d > 0 && d <= 256, "wkv_scan: %d heads of size %d (sizes up to 256)", heads, d);
+    LILY_REQUIRE(heads > 0 && d > 0 && d <= 256, "wkv_scan: %d heads of size %d (sizes up to 256)", heads, d);      // 32 lanes x NPT rows
     LILY_REQUIRE(requests <= 65535, "wkv_scan: %d heads, %d requests", heads, requests);
     int ks = 1;
     while (ks * WKV_NPT < d) ks <<= 1;

@@ -604,12 +604,12 @@ def test_attention_window_edge_and_page_edge(dtype, nq, nkv, d, page):
 
 def test_attention_refuses_what_it_cannot_do():
     o = ops()
-    q = torch.zeros(1, 2 * 272, device=DEV)
-    cache = torch.zeros(2, 2, 2, 16, 272, device=DEV)
+    q = torch.zeros(1, 2 * 704, device=DEV)                     # the CUDA-core kernel takes head sizes up to 640
+    cache = torch.zeros(2, 2, 2, 16, 704, device=DEV)
     table = torch.ones(1, 1, device=DEV, dtype=torch.int32)
     seq = torch.ones(1, device=DEV, dtype=torch.int32)
     with pytest.raises(o.KernelError, match="head_dim"):
-        o.attention_decode(q, cache, table, seq, torch.zeros_like(q), None, 1, 2, 2, 272, 16, 1.0)
+        o.attention_decode(q, cache, table, seq, torch.zeros_like(q), None, 1, 2, 2, 704, 16, 1.0)
     with pytest.raises(o.KernelError, match="CUDA"):
         o.silu_mul(torch.zeros(2, 4))
 
