@@ -43,7 +43,8 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, u
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+    // not volatile: a register operation, which the compiler may move between the (volatile, ordered) fragment loads
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -130,16 +131,18 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const Args
     }
 
     const int* table = a.block_table + (size_t)req * a.bt_stride;
+    // a warp copies whole cached rows (keys warp, warp + 8, ...), its lanes the row's 16-byte pieces: the page of a
+    // row is looked up once, and a piece costs an add and a copy
     auto load_tile = [&](int t, int buf) {
         const int kb = kbeg + t * BN;
         __nv_bfloat16* dst = k_s + (size_t)buf * BN * rowp;
-        for (int i = tid; i < BN * chunks; i += THREADS) {
-            const int j = i / chunks, ch = i % chunks;
+        for (int j = warp; j < BN; j += THREADS / 32) {
             const int kpos = kb + j;
             const bool ok = kpos < kend;
             const __nv_bfloat16* src = a.cache;
-            if (ok) src = a.cache + ((size_t)table[kpos / a.page_size] * a.page_size + kpos % a.page_size) * a.row + ch * 8;
-            cp_async16(smem_u32(dst + (size_t)j * rowp + ch * 8), src, ok);
+            if (ok) src = a.cache + ((size_t)table[kpos / a.page_size] * a.page_size + kpos % a.page_size) * a.row;
+            const uint32_t to = smem_u32(dst + (size_t)j * rowp);
+            for (int ch = lane; ch < chunks; ch += 32) cp_async16(to + ch * 16, ok ? src + ch * 8 : src, ok);
         }
     };
     const int ntiles = kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0;
@@ -174,12 +177,35 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const Args
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
         const unsigned char* kr = kt + (size_t)(wq * 16 + (lane & 7) + ((lane >> 4) << 3)) * rowb + (((lane >> 3) & 1) << 4);
-        for (int kk = 0; kk < ksteps; ++kk) {
-            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-            ldmatrix_x4(smem_u32(qb + kk * 32), a0, a1, a2, a3);
-            ldmatrix_x4(smem_u32(kr + kk * 32), b0, b1, b2, b3);
-            mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
-            mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
+        {
+            // the fragments of the next step are asked for before this step's products are issued; even and odd steps
+            // sum into accumulators of their own, so four products are independent of one another at any time
+            uint32_t a[2][4], b[2][4];
+            float s2[2][4];
+            s2[0][0] = s2[0][1] = s2[0][2] = s2[0][3] = s2[1][0] = s2[1][1] = s2[1][2] = s2[1][3] = 0.f;
+            ldmatrix_x4(smem_u32(qb), a[0][0], a[0][1], a[0][2], a[0][3]);
+            ldmatrix_x4(smem_u32(kr), b[0][0], b[0][1], b[0][2], b[0][3]);
+            int kk = 0;
+            for (; kk + 1 < ksteps; kk += 2) {
+                ldmatrix_x4(smem_u32(qb + (kk + 1) * 32), a[1][0], a[1][1], a[1][2], a[1][3]);
+                ldmatrix_x4(smem_u32(kr + (kk + 1) * 32), b[1][0], b[1][1], b[1][2], b[1][3]);
+                mma_bf16(s[0], a[0][0], a[0][1], a[0][2], a[0][3], b[0][0], b[0][1]);
+                mma_bf16(s[1], a[0][0], a[0][1], a[0][2], a[0][3], b[0][2], b[0][3]);
+                if (kk + 2 < ksteps) {
+                    ldmatrix_x4(smem_u32(qb + (kk + 2) * 32), a[0][0], a[0][1], a[0][2], a[0][3]);
+                    ldmatrix_x4(smem_u32(kr + (kk + 2) * 32), b[0][0], b[0][1], b[0][2], b[0][3]);
+                }
+                mma_bf16(s2[0], a[1][0], a[1][1], a[1][2], a[1][3], b[1][0], b[1][1]);
+                mma_bf16(s2[1], a[1][0], a[1][1], a[1][2], a[1][3], b[1][2], b[1][3]);
+            }
+            if (kk < ksteps) {
+                mma_bf16(s[0], a[0][0], a[0][1], a[0][2], a[0][3], b[0][0], b[0][1]);
+                mma_bf16(s[1], a[0][0], a[0][1], a[0][2], a[0][3], b[0][2], b[0][3]);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] += s2[j][e];
         }
         float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll

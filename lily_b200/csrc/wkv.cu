@@ -84,7 +84,7 @@ __global__ void wkv_decay_kernel(const float* __restrict__ a, int tokens, int ra
 constexpr int WKV_NPT = 8, WKV_PC = 4, WKV_TT = 16, WKV_PAD = 4;
 
 template <typename T>
-__global__ void wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
+__global__ void __launch_bounds__(256, 3) wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
                                 const float* __restrict__ lw, const float* __restrict__ u, float* __restrict__ state,
                                 size_t state_stride, float* __restrict__ y, const int* __restrict__ cu_seqlens,
                                 const int* __restrict__ slots, int heads, int d, int ks, int mode,
