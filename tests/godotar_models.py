@@ -58,6 +58,38 @@ WIDE = {"architecture": "Godotar", "vocab": 257, "width": 128, "norm": {"eps": 1
 DECAY_RANK = 6           # rows of every layer's first decay matrix in these checkpoints (config.json does not say)
 
 
+def random_config(seed: int) -> dict:
+    """A configuration drawn at random: 2 to 5 layers of either mixer in any order, any feed-forward or none, widths
+    in steps of 8, head sizes and ranks in steps of 2 or 8, with and without loop, windows from 3 to 70 or none."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([24, 40, 64, 72, 96, 136])
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        kind = rng.choice(["dense", "moe", "moe", None])
+        mlp = {}
+        if kind == "dense":
+            mlp = {"ff": rng.choice([16, 40, 72])}
+        elif kind == "moe":
+            experts, identity = rng.randint(1, 9), rng.randint(0, 3)
+            mlp = {"ff": rng.choice([8, 24, 40]), "experts": experts, "identity": identity,
+                   "top": rng.randint(1, min(4, experts + identity)), "limit": rng.choice([0.5, 1.0, 7.0])}
+        if rng.random() < 0.5:
+            layers.append(wkv(heads=rng.randint(1, 4), dim=rng.choice([4, 8, 12, 16, 24, 32, 64]), kind=kind, **mlp))
+        else:
+            rot = rng.choice([2, 4, 8, 16])
+            rank = rng.choice([8, 24, 40, 64, 120]) if rng.random() < 0.7 else rng.choice([10, 18, 34])
+            layers.append(latent(heads=rng.randint(1, 6), dim=rng.choice([4, 8, 16, 32]), rot_dim=rot, vdim=rng.choice([4, 8, 20, 32]),
+                                 q_rank=rng.choice([8, 12, 32]), kv_rank=rank, window=rng.choice([None, 3, 17, 40, 70]),
+                                 scale=rng.choice([0.2, 0.5]), base=rng.choice([100.0, 10000.0]), kind=kind, **mlp))
+    cfg = {"architecture": "Godotar", "vocab": rng.choice([61, 128, 300]), "width": width, "norm": {"eps": rng.choice([1e-5, 1e-6])},
+           "logit_scale": rng.choice([0.3, 1.0]), "layers": layers}
+    if rng.random() < 0.7:
+        start = rng.randint(0, len(layers) - 1)
+        cfg["loop"] = {"start": start, "stop": rng.randint(start + 1, len(layers)), "times": rng.randint(1, 3)}
+    return cfg
+
+
 def shapes(cfg: dict) -> Dict[str, tuple]:
     w = cfg["width"]
     out = {"embed": (cfg["vocab"], w), "embed.norm": (w,), "final.norm": (w,)}

@@ -128,6 +128,27 @@ def test_long_decoding_through_graphs(setup, device):
             assert runner.model.graph_safe and runner.graph_steps - before == 70
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(seed):
+    """Ten configurations drawn at random (layer order, sizes, loop, windows, feed-forwards): whole, decoded, in portions
+    and two requests side by side, in both precisions, on whichever kernels their sizes get."""
+    cfg = gm.random_config(seed)
+    with tempfile.TemporaryDirectory() as tmp:
+        weights = gm.make_weights(cfg, 100 + seed)
+        path = gm.write_model_dir(tmp + "/m", cfg, weights)
+        ids, other = gm.tokens(140, cfg["vocab"], seed), gm.tokens(45, cfg["vocab"], seed + 50)
+        for dtype in ("float32", "bfloat16"):
+            want, want_other = plain_logits(cfg, weights, ids, dtype), plain_logits(cfg, weights, other, dtype)
+            runner = runner_for(path, "cuda", dtype, page_size=16 if seed % 2 else 64)
+            close(run_whole(runner, ids), want, dtype, f"whole {cfg}")
+            close(run_portions(runner, ids, [100] + [1] * 40), want, dtype, "decoded")
+            close(run_portions(runner, ids, [2, 33, 1, 2, 70, 1, 1, 30]), want, dtype, "portions")
+            got = run_mixed(runner, {"a": ids, "b": other}, [{"a": 90, "b": 3}, {"a": 1, "b": 40}, {"a": 49, "b": 1}, {"b": 1}])
+            close(got["a"], want, dtype, "beside another")
+            close(got["b"], want_other, dtype, "the other")
+
+
 @pytest.mark.parametrize("device", DEVICES)
 def test_a_slot_used_again_starts_from_nothing(device):
     """A request that takes the slot and pages of one that ended sees nothing of it: neither the heads' matrices, nor
