@@ -60,10 +60,10 @@ DECAY_RANK = 6           # rows of every layer's first decay matrix in these che
 
 def random_config(seed: int) -> dict:
     """A configuration drawn at random: 2 to 5 layers of either mixer in any order, any feed-forward or none, widths
-    in steps of 8, head sizes and ranks in steps of 2 or 8, with and without loop, windows from 3 to 70 or none."""
+    in steps of 8 (and two that are not), head sizes and ranks in steps of 2 or 8, with and without loop, windows from 3 to 70 or none."""
     import random
     rng = random.Random(seed)
-    width = rng.choice([24, 40, 64, 72, 96, 136])
+    width = rng.choice([24, 40, 64, 72, 96, 136, 44, 50])
     layers = []
     for _ in range(rng.randint(2, 5)):
         kind = rng.choice(["dense", "moe", "moe", None])

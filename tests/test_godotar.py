@@ -129,9 +129,9 @@ def test_long_decoding_through_graphs(setup, device):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("seed", range(10))
+@pytest.mark.parametrize("seed", range(24))
 def test_configurations_drawn_at_random(seed):
-    """Ten configurations drawn at random (layer order, sizes, loop, windows, feed-forwards): whole, decoded, in portions
+    """Two dozen configurations drawn at random (layer order, sizes, loop, windows, feed-forwards): whole, decoded, in portions
     and two requests side by side, in both precisions, on whichever kernels their sizes get."""
     cfg = gm.random_config(seed)
     with tempfile.TemporaryDirectory() as tmp:
@@ -187,6 +187,44 @@ def test_greedy_generation_through_the_entry_point(device):
                 assert tok == best or float(logits[best] - logits[tok]) < 1e-3
                 seq.append(tok)
             assert len(res["output_ids"]) == 12
+
+
+@pytest.mark.gpu
+def test_command_line_writes_random_weights_and_generates():
+    """``python -m lily_b200 init-random`` from a config.json that gives the decay's rank, then ``generate`` from the
+    folder it wrote: the tokens are the plain implementation's greedy choice over the written weights."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from lily_b200.weights.safetensors_io import SafetensorsFile
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = copy.deepcopy(gm.VARIED)
+    for layer in cfg["layers"]:
+        if layer["type"] == "wkv":
+            layer["mixer"]["decay_rank"] = 5
+    with tempfile.TemporaryDirectory() as tmp:
+        with open(tmp + "/config.json", "w") as f:
+            json.dump(cfg, f)
+        run = lambda *args: subprocess.run([sys.executable, "-m", "lily_b200", *args], cwd=root, capture_output=True, text=True, timeout=900)
+        out = run("init-random", "--config", tmp + "/config.json", "--out", tmp + "/m", "--seed", "3")
+        assert out.returncode == 0, out.stderr[-2000:]
+        prompt = gm.tokens(19, cfg["vocab"], 8)
+        out = run("generate", "--model-path", tmp + "/m", "--dtype", "float32", "--max-total-tokens", "256", "--page-size", "16",
+                  "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "5", "--ignore-eos")
+        assert out.returncode == 0, out.stderr[-2000:]
+        got = json.loads(out.stdout.strip().splitlines()[-1])["output_ids"]
+        held = SafetensorsFile(tmp + "/m/model.safetensors")
+        weights = {n: held.tensor(n).float() for n in held.entries}
+        seq = list(prompt)
+        for tok in got:
+            logits = plain_logits(cfg, weights, seq)[-1]
+            best = int(torch.argmax(logits))
+            assert tok == best or float(logits[best] - logits[tok]) < 1e-3
+            seq.append(tok)
+        assert len(got) == 5
 
 
 def test_config_refuses_what_the_design_does_not_have():
