@@ -19,17 +19,53 @@ namespace lily {
 // grid (tokens, ceil(width / 256)), block 256: a thread owns one column of one token.  The thread of a request's
 // first new token reads the carried input from the slot and is the one that writes the new one (the input at the
 // request's last new token), so nothing it reads is written by another thread of the launch.
-template <typename T>
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// VEC = 4: a thread owns four neighbouring columns (width and the state's offset and stride multiples of four, aligned
+// bases; the launcher checks); VEC = 1: one column.
+template <typename T, int VEC>
 __global__ void token_shift_mix_kernel(const T* __restrict__ h, int tokens, int width, const float* __restrict__ mu,
                                        int streams, float* __restrict__ state, size_t state_stride, size_t state_off,
                                        const int* __restrict__ cu_seqlens, const int* __restrict__ token_req,
                                        const int* __restrict__ slots, T* __restrict__ out) {
     pdl_enter_small();
     const int t = blockIdx.x;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
     if (c >= width) return;
     const int r = token_req[t];
     const int first = cu_seqlens[r];
+    if (VEC == 4) {
+        const float4 cur = ld4(h + (size_t)t * width + c);
+        float4 prev;
+        if (t == first) {
+            float* st = state + (size_t)slots[r] * state_stride + state_off + c;
+            prev = ld4(st);
+            st4(st, ld4(h + (size_t)(cu_seqlens[r + 1] - 1) * width + c));
+        } else {
+            prev = ld4(h + (size_t)(t - 1) * width + c);
+        }
+        const float4 diff = make_float4(prev.x - cur.x, prev.y - cur.y, prev.z - cur.z, prev.w - cur.w);
+        for (int s = 0; s < streams; ++s) {
+            const float4 m = ld4(mu + (size_t)s * width + c);
+            st4(out + ((size_t)s * tokens + t) * width + c,
+                make_float4(fmaf(diff.x, m.x, cur.x), fmaf(diff.y, m.y, cur.y), fmaf(diff.z, m.z, cur.z), fmaf(diff.w, m.w, cur.w)));
+        }
+        return;
+    }
     const float cur = to_float(h[(size_t)t * width + c]);
     float prev;
     if (t == first) {
@@ -258,21 +294,55 @@ __global__ void wkv_combine_kernel(float* __restrict__ state, size_t state_strid
 // out[t, c] = y[t, c] / rms(y[t, head of c]) * gain[c] * silu(g[t, c]): each group of `gsize` columns is divided by
 // its own root mean square; the gate multiplies the normed value.  grid (tokens, ceil(groups / 4)), block 128: a
 // warp owns one group of one token.
-template <typename T>
+// VEC = 4: `lanes` neighbouring lanes (a power of two, gsize / 4 of them up to a warp) own a group and hold four
+// neighbouring columns a turn, up to four turns, so a warp takes 32 / lanes groups; VEC = 1: a warp a group.
+template <typename T, int VEC>
 __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const T* __restrict__ g, int g_stride,
                                           const float* __restrict__ gain, T* __restrict__ out, int inner, int gsize,
-                                          int groups, float eps) {
+                                          int groups, float eps, int lanes) {
     pdl_enter_small();
     const size_t t = blockIdx.x;
-    const int lane = threadIdx.x & 31, grp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (VEC == 4) {
+        const int li = lane % lanes;
+        const int grp = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / lanes) + lane / lanes;
+        const bool live = grp < groups;
+        const int c0 = (live ? grp : 0) * gsize;
+        const float* yr = y + t * inner + c0;
+        // a group of up to 512 columns stays in the lanes' registers between the two sweeps
+        float4 keep[4];
+        float ssq = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = 4 * (li + lanes * j);
+            keep[j] = (live && i < gsize) ? ld4(yr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            ssq += keep[j].x * keep[j].x + keep[j].y * keep[j].y + keep[j].z * keep[j].z + keep[j].w * keep[j].w;
+        }
+        for (int o = lanes >> 1; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+        if (!live) return;
+        const float inv = rsqrtf(ssq / (float)gsize + eps);
+        const T* gr = g + t * g_stride + c0;
+        T* dst = out + t * inner + c0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = 4 * (li + lanes * j);
+            if (i < gsize) {
+                const float4 z = ld4(gr + i), w = ld4(gain + c0 + i), v = keep[j];
+                st4(dst + i, make_float4(((v.x * inv) * w.x) * (z.x / (1.f + expf(-z.x))), ((v.y * inv) * w.y) * (z.y / (1.f + expf(-z.y))),
+                                         ((v.z * inv) * w.z) * (z.z / (1.f + expf(-z.z))), ((v.w * inv) * w.w) * (z.w / (1.f + expf(-z.w)))));
+            }
+        }
+        return;
+    }
+    const int grp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (grp >= groups) return;
     const int c0 = grp * gsize;
     const float* yr = y + t * inner + c0;
+    const T* gr = g + t * g_stride + c0;
+    T* dst = out + t * inner + c0;
     float ssq = 0.f;
     for (int i = lane; i < gsize; i += 32) ssq = fmaf(yr[i], yr[i], ssq);
     const float inv = rsqrtf(warp_sum(ssq) / (float)gsize + eps);
-    const T* gr = g + t * g_stride + c0;
-    T* dst = out + t * inner + c0;
     for (int i = lane; i < gsize; i += 32) {
         const float z = to_float(gr[i]);
         dst[i] = from_float<T>(((yr[i] * inv) * gain[c0 + i]) * (z / (1.f + expf(-z))));
@@ -288,14 +358,17 @@ LILY_API int lily_token_shift_mix(const void* h, int tokens, int width, const fl
                                   const int* slots, void* out, int dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
     LILY_REQUIRE(width > 0 && streams > 0, "token_shift_mix: width=%d streams=%d", width, streams);
-    dim3 grid(tokens, (width + 255) / 256), block(256);
+    const bool vec = width % 4 == 0 && state_off % 4 == 0 && state_stride % 4 == 0 && (uintptr_t)h % 16 == 0 &&
+                     (uintptr_t)mu % 16 == 0 && (uintptr_t)state % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const int per = vec ? 4 : 1, threads = width / per >= 256 ? 256 : 128;
+    dim3 grid(tokens, (width + threads * per - 1) / (threads * per)), block(threads);
     LILY_REQUIRE(grid.y <= 65535, "token_shift_mix: width %d", width);
-    if (dtype == kBF16)
-        launch_pdl(token_shift_mix_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)h, tokens, width, mu,
-                   streams, state, state_stride, state_off, cu_seqlens, token_req, slots, (__nv_bfloat16*)out);
-    else
-        launch_pdl(token_shift_mix_kernel<float>, grid, block, 0, stream, (const float*)h, tokens, width, mu, streams, state,
-                   state_stride, state_off, cu_seqlens, token_req, slots, (float*)out);
+#define GO(T, V)                                                                                                       \
+    launch_pdl(token_shift_mix_kernel<T, V>, grid, block, 0, stream, (const T*)h, tokens, width, mu, streams, state,    \
+               state_stride, state_off, cu_seqlens, token_req, slots, (T*)out)
+    if (dtype == kBF16) { if (vec) GO(__nv_bfloat16, 4); else GO(__nv_bfloat16, 1); }
+    else { if (vec) GO(float, 4); else GO(float, 1); }
+#undef GO
     LILY_CHECK_LAUNCH("token_shift_mix");
     return 0;
 }
@@ -354,14 +427,22 @@ LILY_API int lily_group_rmsnorm_gate(const float* y, const void* g, int g_stride
                                      int inner, int groups, float eps, int dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
     LILY_REQUIRE(groups >= 1 && inner % groups == 0, "group_rmsnorm_gate: %d columns in %d groups", inner, groups);
-    dim3 grid(tokens, (groups + 3) / 4), block(128);
+    const int gsize = inner / groups;
+    const size_t item = dtype == kBF16 ? 2 : 4;
+    int lanes = 32;                                               // lanes a group in the vector form: gsize / 4, up to a warp
+    while (lanes > 1 && lanes * 4 > gsize) lanes >>= 1;
+    const bool vec = gsize % 4 == 0 && gsize <= 16 * lanes && g_stride % 4 == 0 &&
+                     (uintptr_t)y % 16 == 0 && (uintptr_t)gain % 16 == 0 && (uintptr_t)g % (4 * item) == 0 &&
+                     (uintptr_t)out % (4 * item) == 0;
+    const int per_block = vec ? 4 * (32 / lanes) : 4;              // groups a block of four warps takes
+    dim3 grid(tokens, (groups + per_block - 1) / per_block), block(128);
     LILY_REQUIRE(grid.y <= 65535, "group_rmsnorm_gate: %d groups", groups);
-    if (dtype == kBF16)
-        launch_pdl(group_rmsnorm_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, y, (const __nv_bfloat16*)g, g_stride, gain,
-                   (__nv_bfloat16*)out, inner, inner / groups, groups, eps);
-    else
-        launch_pdl(group_rmsnorm_gate_kernel<float>, grid, block, 0, stream, y, (const float*)g, g_stride, gain, (float*)out,
-                   inner, inner / groups, groups, eps);
+#define GO(T, V)                                                                                                    \
+    launch_pdl(group_rmsnorm_gate_kernel<T, V>, grid, block, 0, stream, y, (const T*)g, g_stride, gain, (T*)out, inner, \
+               gsize, groups, eps, lanes)
+    if (dtype == kBF16) { if (vec) GO(__nv_bfloat16, 4); else GO(__nv_bfloat16, 1); }
+    else { if (vec) GO(float, 4); else GO(float, 1); }
+#undef GO
     LILY_CHECK_LAUNCH("group_rmsnorm_gate");
     return 0;
 }
