@@ -14,7 +14,6 @@ vector added to ``x`` ahead of it.  The logits are ``logit_scale * E nrm(x, w_fi
 
 from __future__ import annotations
 
-import math
 from typing import Dict, List, Optional, Tuple
 
 import torch
