@@ -53,6 +53,8 @@ def build_spec(cfg: GodotarConfig) -> ModelSpec:
         blocks.append(ParallelBlockSpec(prefix=f"l{i}", hidden_size=cfg.width, mixers=(("mix", mixer, None),),
                                         feed_forward=ff, norm=norm, eps=cfg.eps, ff_norm=norm if ff is not None else None))
     schedule = [ScheduleEntry(i, step=None if t is None else (STEP_TENSOR, t)) for i, t in cfg.runs()]
+    if cfg.loop is not None and all(entry.step is None for entry in schedule):
+        ignored.append(STEP_TENSOR)                         # a loop over no layer has no pass to add its vectors ahead of
     return ModelSpec(architecture=cfg.architecture, vocab_size=cfg.vocab, hidden_size=cfg.width, blocks=blocks,
                      schedule=schedule, final_norm=norm, embed_name="embed", final_norm_prefix="final.norm", head_name=None,
                      max_position=cfg.max_positions, ignored_tensors=tuple(ignored), logit_scale=cfg.logit_scale,
