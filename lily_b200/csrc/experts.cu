@@ -20,89 +20,132 @@ namespace lily {
 constexpr int ROUTE_MAX = 1024;       // router outputs
 constexpr int ROUTE_TOP_MAX = 64;
 
-// grid (tokens), block 128.
-template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, int width, const float* __restrict__ router,
+// grid (ceil(tokens / TB)), block 128: a block takes TB tokens, so a number of the router matrix read once serves TB
+// sums (one token a block rereads the matrix from L2 for every token: 50 us for 2,048 tokens of 2,048 columns).
+// A token's logits are summed in the same order whatever TB is.
+template <typename T, int TB>
+__global__ void moe_route_kernel(const T* __restrict__ h, int tokens, int width, const float* __restrict__ router,
                                  const float* __restrict__ correction, int outputs, int top, int* __restrict__ chosen,
                                  float* __restrict__ weights) {
-    __shared__ float s[ROUTE_MAX];
-    __shared__ float picked[ROUTE_TOP_MAX];
-    extern __shared__ __align__(16) float xs[];              // [width]: the token's row
+    __shared__ float picked[4][ROUTE_TOP_MAX];
+    extern __shared__ __align__(16) float dyn[];             // [TB][width] the tokens' rows, then [TB][outputs] their scores
+    float* xs = dyn;
+    float* sc = dyn + (size_t)TB * width;
     pdl_enter_small();
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    const T* x = h + (size_t)t * width;
-    // the token's row once into shared memory as float32; then every warp's outputs read it from there, eight columns
-    // a lane and turn with all their loads asked for ahead of the sums (a plain loop waits for memory at every step)
-    for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_float(x[c]);
+    const int t0 = blockIdx.x * TB, nt = min(TB, tokens - t0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    // the tokens' rows into shared memory as float32, 16 bytes a load where the rows allow (a plain loop of single
+    // numbers waits for memory a hundred times over)
+    const T* src = h + (size_t)t0 * width;
+    constexpr int PER = 16 / (int)sizeof(T);
+    if (width % PER == 0 && ((uintptr_t)h & 15) == 0) {
+        for (int i = threadIdx.x * PER; i < TB * width; i += blockDim.x * PER) {
+            float v[PER];
+            if (i < nt * width) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+                const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int u = 0; u < PER; ++u) v[u] = to_float(e[u]);
+            } else {
+#pragma unroll
+                for (int u = 0; u < PER; ++u) v[u] = 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < PER; u += 4) *reinterpret_cast<float4*>(xs + i + u) = make_float4(v[u], v[u + 1], v[u + 2], v[u + 3]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < TB * width; i += blockDim.x) xs[i] = i < nt * width ? to_float(src[i]) : 0.f;
+    }
     __syncthreads();
     for (int e = warp; e < outputs; e += nwarp) {
         const float* w = router + (size_t)e * width;
-        float z = 0.f;
-        int c = lane * 4;
+        float z[TB];
+#pragma unroll
+        for (int j = 0; j < TB; ++j) z[j] = 0.f;
         if ((width & 3) == 0) {
-            float4 wv[4], xv[4];
+            // four columns a lane and turn, four turns' numbers of the matrix asked for ahead of their sums
+            int c = lane * 4;
             for (; c + 3 * 128 < width; c += 4 * 128) {
+                float4 wv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) wv[u] = *reinterpret_cast<const float4*>(w + c + u * 128);
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    wv[u] = *reinterpret_cast<const float4*>(w + c + u * 128);
-                    xv[u] = *reinterpret_cast<const float4*>(xs + c + u * 128);
-                }
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    z = fmaf(xv[u].x, wv[u].x, fmaf(xv[u].y, wv[u].y, fmaf(xv[u].z, wv[u].z, fmaf(xv[u].w, wv[u].w, z))));
+                    for (int j = 0; j < TB; ++j) {
+                        const float4 x0 = *reinterpret_cast<const float4*>(xs + j * width + c + u * 128);
+                        z[j] = fmaf(x0.x, wv[u].x, fmaf(x0.y, wv[u].y, fmaf(x0.z, wv[u].z, fmaf(x0.w, wv[u].w, z[j]))));
+                    }
+                }
             }
             for (; c < width; c += 128) {
-                const float4 wq = *reinterpret_cast<const float4*>(w + c), xq = *reinterpret_cast<const float4*>(xs + c);
-                z = fmaf(xq.x, wq.x, fmaf(xq.y, wq.y, fmaf(xq.z, wq.z, fmaf(xq.w, wq.w, z))));
+                const float4 w0 = *reinterpret_cast<const float4*>(w + c);
+#pragma unroll
+                for (int j = 0; j < TB; ++j) {
+                    const float4 x0 = *reinterpret_cast<const float4*>(xs + j * width + c);
+                    z[j] = fmaf(x0.x, w0.x, fmaf(x0.y, w0.y, fmaf(x0.z, w0.z, fmaf(x0.w, w0.w, z[j]))));
+                }
             }
         } else {
-            for (c = lane; c < width; c += 32) z = fmaf(xs[c], w[c], z);
+            for (int c = lane; c < width; c += 32) {
+                const float wv = w[c];
+#pragma unroll
+                for (int j = 0; j < TB; ++j) z[j] = fmaf(xs[j * width + c], wv, z[j]);
+            }
         }
-        z = warp_sum(z);
-        if (lane == 0) s[e] = z;
+#pragma unroll
+        for (int j = 0; j < TB; ++j) {
+            const float total = warp_sum(z[j]);
+            if (lane == 0) sc[j * outputs + e] = total;
+        }
     }
     __syncthreads();
-    if (warp != 0) return;
-    float mx = -INFINITY;
-    for (int e = lane; e < outputs; e += 32) mx = fmaxf(mx, s[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < outputs; e += 32) {
-        const float p = expf(s[e] - mx);
-        s[e] = p;
-        sum += p;
-    }
-    sum = warp_sum(sum);
-    const float inv = 1.f / sum;
-    __syncwarp();
-    float total = 0.f;
-    for (int k = 0; k < top; ++k) {
-        float best = -INFINITY;
-        int at = outputs;
+    // softmax and choice: a warp a token
+    for (int j = warp; j < nt; j += nwarp) {
+        float* s = sc + j * outputs;
+        const int t = t0 + j;
+        float mx = -INFINITY;
+        for (int e = lane; e < outputs; e += 32) mx = fmaxf(mx, s[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
         for (int e = lane; e < outputs; e += 32) {
-            const float p = s[e];
-            if (p < 0.f) continue;                                // taken already
-            const float c = p * inv + correction[e];
-            if (c > best) { best = c; at = e; }
+            const float p = expf(s[e] - mx);
+            s[e] = p;
+            sum += p;
         }
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
-        }
-        if (at >= outputs) at = 0;                                // cannot happen while top <= outputs
-        const float p = s[at] * inv;
-        total += p;
+        sum = warp_sum(sum);
+        const float inv = 1.f / sum;
         __syncwarp();
-        if (lane == 0) {
-            chosen[(size_t)t * top + k] = at;
-            picked[k] = p;
-            s[at] = -1.f;
+        float total = 0.f;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int at = outputs;
+            for (int e = lane; e < outputs; e += 32) {
+                const float p = s[e];
+                if (p < 0.f) continue;                                // taken already
+                const float c = p * inv + correction[e];
+                if (c > best) { best = c; at = e; }
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (at >= outputs) at = 0;                                // cannot happen while top <= outputs
+            const float p = s[at] * inv;
+            total += p;
+            __syncwarp();
+            if (lane == 0) {
+                chosen[(size_t)t * top + k] = at;
+                picked[warp][k] = p;
+                s[at] = -1.f;
+            }
+            __syncwarp();
         }
+        const float norm = 1.f / (total + 1e-20f);
+        for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] = picked[warp][k] * norm;
         __syncwarp();
     }
-    const float norm = 1.f / (total + 1e-20f);
-    for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] = picked[k] * norm;
 }
 
 // One block of 1024 threads.  chosen [pairs]; experts: router outputs that have weights (the rest are skipped here).
@@ -303,13 +346,17 @@ LILY_API int lily_moe_route(const void* h, int tokens, int width, const float* r
     if (tokens == 0) return 0;
     LILY_REQUIRE(outputs >= 1 && outputs <= ROUTE_MAX, "moe_route: %d router outputs (up to %d)", outputs, ROUTE_MAX);
     LILY_REQUIRE(top >= 1 && top <= outputs && top <= ROUTE_TOP_MAX, "moe_route: top %d of %d", top, outputs);
-    LILY_REQUIRE(width > 0 && width <= 10240, "moe_route: rows of %d numbers (up to 10240)", width);
-    if (dtype == kBF16)
-        launch_pdl(moe_route_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), (size_t)width * sizeof(float), stream, (const __nv_bfloat16*)h, width, router,
-                   correction, outputs, top, chosen, weights);
-    else
-        launch_pdl(moe_route_kernel<float>, dim3(tokens), dim3(128), (size_t)width * sizeof(float), stream, (const float*)h, width, router, correction,
-                   outputs, top, chosen, weights);
+    // four tokens a block once there are blocks enough for the device, and while their rows fit the shared memory
+    const int tb = (tokens >= 1024 && (size_t)(4 * width + 4 * outputs) * sizeof(float) <= 40 * 1024) ? 4 : 1;
+    const size_t smem = (size_t)tb * (width + outputs) * sizeof(float);
+    LILY_REQUIRE(width > 0 && smem <= 44 * 1024, "moe_route: rows of %d numbers and %d outputs do not fit a block's shared memory", width, outputs);
+    dim3 grid((tokens + tb - 1) / tb), block(128);
+#define GO(T, TB)                                                                                                   \
+    launch_pdl(moe_route_kernel<T, TB>, grid, block, smem, stream, (const T*)h, tokens, width, router, correction, outputs, \
+               top, chosen, weights)
+    if (dtype == kBF16) { if (tb == 4) GO(__nv_bfloat16, 4); else GO(__nv_bfloat16, 1); }
+    else { if (tb == 4) GO(float, 4); else GO(float, 1); }
+#undef GO
     LILY_CHECK_LAUNCH("moe_route");
     return 0;
 }

@@ -383,6 +383,13 @@ def test_routed_experts(device, experts, identity, top, ff, width):
             got = ops.moe_experts(xs, routing, gu, dn, 0.9, 1.702).cpu()
             tol = 1e-5 if dtype == torch.float32 else 2e-2
             assert float((got - want[rows]).abs().max()) < tol * max(1.0, float(want.abs().max())), (dtype, rows)
+    # many tokens (several share a block on the GPU): the same choices and weights as the plain router
+    big = torch.randn(1100, width, generator=g)
+    routing = ops.moe_route(big.to(device), w["p.router"].to(device), w["p.correction"].to(device), top, experts)
+    chosen_big, weights_big = pg.route(big, w, "p", top)
+    assert torch.equal(routing.chosen.cpu().long().sort(-1).values, chosen_big.sort(-1).values)
+    order = routing.chosen.cpu().long().argsort(-1)
+    assert float((routing.weights.cpu().gather(1, order) - weights_big.gather(1, chosen_big.argsort(-1))).abs().max()) < 1e-5
     # the construction does what it says: corrections change choices, clamps bite, identity outputs are chosen
     s = torch.softmax(h @ w["p.router"].t(), -1)
     if outputs > top:
