@@ -5,7 +5,9 @@
 //
 // The query rows of a request are its (token, head) pairs in that order, which is how they lie in memory.  A block
 // takes 32 consecutive rows of a tile of `tile_tokens` new tokens (grid: tiles x ceil(tile_tokens * heads / 32) x
-// key ranges) and walks the keys its rows can see in tiles of 64, double-buffered with cp.async.  Eight warps: warp w
+// key ranges) and walks the keys its rows can see in tiles of 64, double-buffered: a cached row is one bulk copy
+// (cp.async.bulk, completion counted in bytes on an mbarrier of the buffer), issued by the lanes of the first warp.
+// Eight warps: warp w
 // owns the 16 rows of row tile w / 4 and, of a key tile, the 16 keys w % 4 for the scores and the value columns
 // [w % 4] * VT * 8 ... for the weighted sum.  Per key tile the four warps of a row tile exchange row maxima, the
 // weights (bfloat16) and row sums through shared memory, so no score is computed twice.
@@ -15,6 +17,8 @@
 // (lily_attention_combine: [requests, heads, ranges, rank] outputs, then [.., 2]).
 //
 // Scores, softmax and sums are float32; the weights are rounded to bfloat16 for their product with the values.
+// The wait for a tile is bounded: when it runs out the block records it in a status word (lily_latent_attention_status),
+// gives the copies it still has in flight a bounded wait and returns.
 #include "attention_args.cuh"
 #include "common.cuh"
 
@@ -27,12 +31,26 @@ constexpr int THREADS = 256;
 constexpr int PSTRIDE = BN + 8;   // bfloat16 per row of the weights' tile
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
-    const int n = valid ? 16 : 0;     // 0 source bytes: the 16 destination bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+constexpr uint32_t SPIN_LIMIT = 1u << 22;     // polls before a wait for a tile gives up (a fraction of a second)
+__device__ int g_status = 0;                  // 0 ok; else 1 + the block of the first wait that gave up
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// `bytes` (a multiple of 16) from global to shared memory, both 16-byte aligned; completes on the mbarrier
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -81,6 +99,8 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const Args
     __nv_bfloat16* p_s = k_s + 2 * BN * rowp;                       // [2 row tiles][16][PSTRIDE]
     float* smax = reinterpret_cast<float*>(p_s + 2 * 16 * PSTRIDE); // [2][4][16]
     float* ssum = smax + 2 * 4 * 16;                                // [2][4][16]
+    __shared__ __align__(8) uint64_t kbar[2];                       // a key buffer's copies have landed
+    __shared__ int abort_s;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int mt = warp >> 2, wq = warp & 3;
     const int c = lane & 3, r_lo = lane >> 2, r_hi = r_lo + 8;
@@ -131,23 +151,36 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const Args
     }
 
     const int* table = a.block_table + (size_t)req * a.bt_stride;
-    // a warp copies whole cached rows (keys warp, warp + 8, ...), its lanes the row's 16-byte pieces: the page of a
-    // row is looked up once, and a piece costs an add and a copy
+    // the first warp's lanes copy whole cached rows, a bulk copy a row; rows past the last key are zeroed by hand
+    const uint32_t bar0 = smem_u32(&kbar[0]);
+    const uint32_t row_bytes = (uint32_t)a.row * 2;
     auto load_tile = [&](int t, int buf) {
+        if (warp != 0) return;
         const int kb = kbeg + t * BN;
+        const int valid = min(BN, kend - kb);
+        const uint32_t bar = bar0 + 8 * buf;
         __nv_bfloat16* dst = k_s + (size_t)buf * BN * rowp;
-        for (int j = warp; j < BN; j += THREADS / 32) {
-            const int kpos = kb + j;
-            const bool ok = kpos < kend;
-            const __nv_bfloat16* src = a.cache;
-            if (ok) src = a.cache + ((size_t)table[kpos / a.page_size] * a.page_size + kpos % a.page_size) * a.row;
-            const uint32_t to = smem_u32(dst + (size_t)j * rowp);
-            for (int ch = lane; ch < chunks; ch += 32) cp_async16(to + ch * 16, ok ? src + ch * 8 : src, ok);
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)valid * row_bytes);
+        __syncwarp();
+        for (int j = lane; j < BN; j += 32) {
+            if (j < valid) {
+                const int kpos = kb + j;
+                const __nv_bfloat16* src = a.cache + ((size_t)table[kpos / a.page_size] * a.page_size + kpos % a.page_size) * a.row;
+                bulk_copy(smem_u32(dst + (size_t)j * rowp), src, row_bytes, bar);
+            } else {
+                for (int ch = 0; ch < chunks; ++ch) *reinterpret_cast<uint4*>(dst + (size_t)j * rowp + ch * 8) = make_uint4(0, 0, 0, 0);
+            }
         }
     };
     const int ntiles = kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0;
+    if (tid == 0) {
+        abort_s = 0;
+        mbar_init(bar0, 1);
+        mbar_init(bar0 + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();                                        // the barriers are set up (and the queries staged)
     if (ntiles > 0) load_tile(0, 0);
-    cp_async_commit();
 
     // positions of this thread's two rows (rows beyond the tile see nothing)
     const int gr_lo = row0 + mt * 16 + r_lo, gr_hi = row0 + mt * 16 + r_hi;
@@ -166,10 +199,27 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(const Args
 
     for (int t = 0; t < ntiles; ++t) {
         const int buf = t & 1;
-        cp_async_wait<0>();
-        __syncthreads();                                    // tile t has landed; everyone is done with tile t - 1
+        {
+            // tile t has landed when its buffer's barrier has passed the phase of this use
+            const uint32_t bar = bar0 + 8 * buf, parity = (uint32_t)(t >> 1) & 1;
+            bool ok = false;
+            for (uint32_t i = 0; i < SPIN_LIMIT && !ok; ++i) {
+                ok = mbar_try_wait(bar, parity);
+                if (!ok && (i & 1023u) == 1023u && *(volatile int*)&abort_s) break;
+            }
+            if (!ok) {
+                abort_s = 1;
+                atomicCAS(&g_status, 0, 1 + (int)(blockIdx.x + blockIdx.y * gridDim.x));
+            }
+        }
+        __syncthreads();                                    // everyone has tile t and is done with tile t - 1
+        if (*(volatile int*)&abort_s) {
+            // a copy of the tile asked for ahead may still be on its way into this block's shared memory
+            if (tid == 0)
+                for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(bar0 + 8 * buf, (uint32_t)(t >> 1) & 1); ++i) {}
+            return;
+        }
         if (t + 1 < ntiles) load_tile(t + 1, buf ^ 1);
-        cp_async_commit();
         const unsigned char* kt = reinterpret_cast<const unsigned char*>(k_s + (size_t)buf * BN * rowp);
         const int kb = kbeg + t * BN;
 
@@ -412,4 +462,13 @@ LILY_API int lily_latent_attention_decode_mma(const void* q, const void* cache, 
     if (int rc = launch<true>(a, grid, stream)) return rc;
     LILY_CHECK_LAUNCH("latent_attention_decode");
     return 0;
+}
+
+// 0, or 1 + the block of the first wait for a key tile that gave up (then cleared).  Synchronises the device.
+LILY_API int lily_latent_attention_status() {
+    int v = 0, zero = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, latent::g_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(latent::g_status, &zero, sizeof(int));
+    return v;
 }

@@ -115,6 +115,7 @@ def library():
         lib.lily_latent_attention_mma_takes.restype = _i
         lib.lily_latent_attention_mma_tile_tokens.argtypes = [_i]
         lib.lily_latent_attention_mma_tile_tokens.restype = _i
+        lib.lily_latent_attention_status.restype = _i
         lib.lily_moe_tile_rows.restype = _i
         _lib = lib
     return _lib
@@ -547,6 +548,12 @@ def latent_tensor_cores(dtype: torch.dtype, d: int, dv: Optional[int], nkv: int 
     (bfloat16, one shared row a position, rows of whole 16-byte pieces, an even value width of up to 512, plain scores)."""
     return (dtype == torch.bfloat16 and nkv == 1 and not softcap and dv is not None and not _SIMT_LATENT
             and bool(library().lily_latent_attention_mma_takes(int(d), int(dv))))
+
+
+def latent_attention_status() -> int:
+    """0, or 1 + the block of the first bounded wait for a key tile that gave up in the tensor-core kernel for cached
+    latents (synchronises; the word is cleared when read)."""
+    return int(library().lily_latent_attention_status())
 
 
 def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size: int = 0, new_tokens: int = 0,

@@ -288,6 +288,8 @@ def test_one_position_that_stands_out(device, heads, d, rot, dv, q_rank, rank, w
             got = run_latent(ops, device, dtype, h, w, c, eps, page, cuts)
             tol = 5e-5 if dtype == torch.float32 else 6e-2
             assert float((got - want).abs().max()) < tol * max(1.0, float(want.abs().max())), (dtype, cuts[:3])
+    if device == "cuda":
+        assert ops.latent_attention_status() == 0                 # no bounded wait of the tensor-core kernel ran out
 
 
 @pytest.mark.gpu
@@ -326,6 +328,7 @@ def test_latent_decode_in_key_ranges(heads, row, rank, window):
                                  window, dv=rank, values_in_keys=True)
             tol = 1e-5 if dtype == torch.float32 else 2e-2
             assert float((out.float().cpu().view(len(lens), heads, rank) - want).abs().max()) < tol * float(want.abs().max()), (dtype, splits)
+    assert ops.latent_attention_status() == 0                     # no bounded wait of the tensor-core kernel ran out
 
 
 @pytest.mark.parametrize("device", DEVICES)
