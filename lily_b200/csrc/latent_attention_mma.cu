@@ -391,7 +391,7 @@ static int launch(const Args& a, dim3 grid, cudaStream_t stream) {
 #define CASE(N)                                                                                                       \
     case N: {                                                                                                         \
         auto kern = latent_attention_kernel<N, DECODE>;                                                               \
-        static size_t granted = 48 * 1024;      /* set once per size, never while a graph is captured */               \
+        static size_t granted = 47 * 1024;      /* beside the kernel's static shared memory; set once per size */      \
         if (smem > granted) {                                                                                         \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
             if (e != cudaSuccess) { set_error("latent attention: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return 2; } \
