@@ -260,7 +260,8 @@ def run_latent(ops, device, dtype, h, w, c, eps, page, cuts):
 
 @pytest.mark.parametrize("device", DEVICES)
 @pytest.mark.parametrize("heads,d,rot,dv,q_rank,rank", [(3, 8, 4, 12, 20, 24), (2, 32, 16, 32, 48, 128), (1, 16, 2, 5, 9, 33),
-                                                        (5, 12, 32, 8, 16, 72), (40, 16, 64, 16, 32, 512), (16, 8, 8, 8, 24, 264)])
+                                                        (5, 12, 32, 8, 16, 72), (40, 16, 64, 16, 32, 512), (16, 8, 8, 8, 24, 264),
+                                                        (4, 32, 16, 24, 32, 64)])
 @pytest.mark.parametrize("window", [37, None, 64])
 def test_one_position_that_stands_out(device, heads, d, rot, dv, q_rank, rank, window):
     """The inputs at three positions (at a page border and far back) are made so that their cached latent scores high
@@ -293,7 +294,8 @@ def test_one_position_that_stands_out(device, heads, d, rot, dv, q_rank, rank, w
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("heads,row,rank", [(4, 144, 128), (16, 576, 512), (33, 72, 40), (3, 28, 24)])
+@pytest.mark.parametrize("heads,row,rank", [(4, 144, 128), (16, 576, 512), (33, 72, 40), (3, 28, 24), (4, 80, 64), (2, 136, 128),
+                                            (5, 264, 256), (8, 392, 384), (2, 520, 512), (1, 16, 8), (6, 24, 16), (3, 200, 130)])
 @pytest.mark.parametrize("window", [None, 100])
 def test_latent_decode_in_key_ranges(heads, row, rank, window):
     """One new token a request over cached rows of unequal lengths, the keys cut into 1 to 7 ranges that are merged
